@@ -157,6 +157,15 @@ _CUDA_SIG = {
     "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),
     "ggb_op_moe_linear": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, vp, i32, vp, i64]),
     "ggb_op_moe_combine": (i32, [vp, vp, vp, i64, i32, i32, i64, vp]),
+    "ggb_op_moe_route_sigmoid": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, i32, i32, vp, vp, vp]),
+    "ggb_op_embed_pos": (i32, [i32, vp, vp, vp, vp, i64, i64, f32, vp]),
+    "ggb_op_norm_add_norm": (i32, [i32, vp, vp, vp, f32, i64, i64, vp, vp, vp]),
+    "ggb_op_causal_conv_bias": (i32, [i32, vp, i64, i64, i64, vp, vp, i32, i32, i32, vp, vp, i64, vp]),
+    "ggb_op_latent_attn_window": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i64, i32, vp]),
+    "ggb_op_latent_attn_out_gated": (i32, [i32, vp, i32, vp, vp, i64, i32, i32, i32, vp, i64, vp]),
+    "ggb_op_sigmoid_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, i32, f32, f32, vp, vp, i32, vp, vp]),
+    "ggb_sigmoid_attn_scratch_bytes": (sz, [i32]),
+    "ggb_op_sigmoid_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp]),
     "ggb_comm_unique_id": (i32, [vp]), "ggb_comm_init": (i32, [vp, i32, i32]), "ggb_comm_destroy": (i32, []),
     "ggb_comm_rank": (i32, []), "ggb_comm_size": (i32, []), "ggb_op_allgather": (i32, [vp, vp, sz]),
 }
@@ -196,6 +205,7 @@ _HOST_SIG = {
     "lm_architectures_csv": (i32, [C.c_char_p, i32]),
     "sf_config_probe": (i32, [C.c_char_p, P(i64)]),
     "bg_config_probe": (i32, [C.c_char_p, P(i64)]),
+    "dl_config_probe": (i32, [C.c_char_p, P(i64)]),
     "st_probe": (i32, [C.c_char_p, C.c_char_p, P(i64), P(i64), C.c_char_p, i32, P(i64)]),
     "mul_mat": (None, [i64, i64, i64, i64, i64, i64, i64, sz, i64, vp, vp, vp, vp, i32, vp]),
     "init_cuda_offload": (i32, [i32]),

@@ -189,7 +189,7 @@ template <typename E, int RC, int TQ>
 __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *__restrict__ qa, const E *__restrict__ cache, int64_t ldk,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
                                                                   int T, int H, int R, int Dr, int n_split, int SW, int hpc,
-                                                                  float *__restrict__ part) {
+                                                                  int64_t window, float *__restrict__ part) {
     // TQ consecutive tokens per CTA (portions): a warp scores and accumulates its head for all of them from ONE read of
     // every tile word; the later token's extra position is masked for the earlier one.
     extern __shared__ __align__(16) uint32_t la_smem[];
@@ -203,8 +203,10 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
     const int t0 = blockIdx.x * TQ, split = blockIdx.y;
     const int nq = min(TQ, T - t0);
     const int64_t n_kv0 = (int64_t)*pos0 + t0 + 1; // causal: token t0 + u sees positions < n_kv0 + u
-    // tiles of 32 positions are dealt to the splits in turn: split s takes tiles s, s + n_split, ...
-    const int64_t j0 = (int64_t)split * 32, j1 = n_kv0 + nq - 1, jstep = (int64_t)32 * n_split;
+    // tiles of 32 positions are dealt to the splits in turn: split s takes tiles s, s + n_split, ... counted from the tile
+    // that holds the first position the CTA's first token sees (window > 0: token i sees i - window < j <= i)
+    const int64_t jlo = window > 0 ? max((int64_t)0, n_kv0 - window) / 32 * 32 : 0;
+    const int64_t j0 = jlo + (int64_t)split * 32, j1 = n_kv0 + nq - 1, jstep = (int64_t)32 * n_split;
     const int h_begin = blockIdx.z * hpc, h_end = min(H, h_begin + hpc);
     for (int h0 = h_begin; h0 < h_end; h0 += NW) {
         const int h = h0 + warp;
@@ -278,7 +280,8 @@ __global__ void __launch_bounds__(512) latent_attn_partial_kernel(const float *_
                     for (int u = 0; u < TQ; u++) a4[u][0] = TileWord<E>::dot(tr[w], qh + u * QKp + w * PER, a4[u][0]);
 #pragma unroll
                 for (int u = 0; u < TQ; u++)
-                    if (j + lane < n_kv0 + u && u < nq) s[u] = (a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]);
+                    if (j + lane < n_kv0 + u && u < nq && (window <= 0 || j + lane >= n_kv0 + u - window))
+                        s[u] = (a4[u][0] + a4[u][1]) + (a4[u][2] + a4[u][3]);
             }
             float p[TQ];
 #pragma unroll
@@ -323,12 +326,12 @@ constexpr int kOutT = 8; // tokens of one head per CTA; v_chunk outputs per CTA 
 template <typename E>
 __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__restrict__ part, int n_split, const float *__restrict__ sink,
                                                               const E *__restrict__ w_uv, int64_t T, int H, int R, int Dv,
-                                                              int v_chunk, E *__restrict__ out) {
+                                                              int v_chunk, const float *__restrict__ gate, int64_t ldg, E *__restrict__ out) {
     extern __shared__ __align__(16) float ol[]; // [kOutT][R]
     const int h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t t0 = (int64_t)blockIdx.x * kOutT;
     const int nt = (int)min((int64_t)kOutT, T - t0);
-    const float sk = sink[h];
+    const float sk = sink ? sink[h] : -INFINITY; // no sink: nothing beside the keys in the denominator
     float *wsm = ol + kOutT * R; // [kOutT][n_split] weight of every split: exp(m_s - M) / L
     const int64_t ps = (int64_t)H * (R + 2);
     if (warp < nt) { // one warp per token: maximum and denominator over the splits and the sink
@@ -338,7 +341,8 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
         M = warp_max_f32(M);
         float L = 0.f;
         for (int s = lane; s < n_split; s += 32) L = fmaf(p0[s * ps + 1], expf(p0[s * ps] - M), L);
-        L = warp_sum_f32(L) + expf(sk - M);
+        L = warp_sum_f32(L);
+        if (sink) L += expf(sk - M);
         const float inv = 1.0f / L;
         for (int s = lane; s < n_split; s += 32) wsm[warp * n_split + s] = expf(p0[s * ps] - M) * inv;
     }
@@ -397,14 +401,18 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
 #pragma unroll
         for (int tt = 0; tt < kOutT; tt++) {
             const float s = warp_sum_f32(acc[tt]);
-            if (lane == 0 && tt < nt) out[(t0 + tt) * ((int64_t)H * Dv) + (int64_t)h * Dv + v] = from_f32<E>(s);
+            if (lane == 0 && tt < nt) {
+                // the head's gate: one number per (token, head), sigmoid in fp32
+                const float gsc = gate ? 1.0f / (1.0f + expf(-gate[(t0 + tt) * ldg + h])) : 1.0f;
+                out[(t0 + tt) * ((int64_t)H * Dv) + (int64_t)h * Dv + v] = from_f32<E>(gate ? s * gsc : s);
+            }
         }
     }
 }
 
 template <typename E>
 int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const int32_t *table, int B, const int32_t *pos0, int64_t T, int H,
-                        int R, int Dr, int n_split, float *part) {
+                        int R, int Dr, int n_split, int64_t window, float *part) {
     constexpr int PER = TileWord<E>::per;
     const int words = (R + Dr + PER - 1) / PER, SW = words | 1; // odd row pitch: lanes of a warp hit 32 different banks
     // heads per CTA: all of them (one warp each, up to 16 at a time) when many tokens share the GPU, groups of 4 when a
@@ -419,7 +427,7 @@ int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const i
     {                                                                                                                        \
         auto k = latent_attn_partial_kernel<E, RC, TQ>;                                                                      \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));     \
-        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, (int)T, H, R, Dr, n_split, SW, hpc, part); \
+        k<<<grid, NW * 32, smem, ggb_cuda_stream()>>>(qa, (const E *)cache, ldk, table, B, pos0, (int)T, H, R, Dr, n_split, SW, hpc, window, part); \
     }
 #define LA_CASE(RC)                       \
     {                                     \
@@ -449,7 +457,7 @@ int ggb_op_latent_kv_store(int dt, const float *d, int64_t ldd, int64_t T, int R
                            const float *cos_sin, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(d && norm_w && cos_sin && pos0 && block_table && cache && T > 0 && R > 0 && Dr >= 0 && block_size > 0 &&
+    GGB_CHECK_ARG(d && norm_w && (cos_sin || !rot_dims) && pos0 && block_table && cache && T > 0 && R > 0 && Dr >= 0 && block_size > 0 &&
                       rot_dims >= 0 && rot_dims <= Dr && rot_dims % 2 == 0,
                   "latent_kv_store: bad arguments");
     const int64_t ldk = ggb_latent_cache_ld(R, Dr);
@@ -467,7 +475,7 @@ int ggb_op_latent_q_absorb(int dt, const float *q, int64_t ldq, int64_t T, int H
                            const int32_t *pos0, const void *w_uk, int R, float scale, float *qa) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(q && cos_sin && pos0 && w_uk && qa && T > 0 && H > 0 && D > 0 && R > 0 && rot_dims <= Dr && rot_dims % 2 == 0,
+    GGB_CHECK_ARG(q && (cos_sin || !rot_dims) && pos0 && w_uk && qa && T > 0 && H > 0 && D > 0 && R > 0 && rot_dims <= Dr && rot_dims % 2 == 0,
                   "latent_q_absorb: bad arguments");
     const dim3 grid((unsigned)((T + kAbsT - 1) / kAbsT), (unsigned)H, (unsigned)((R + 63) / 64));
     const size_t smem = (size_t)kAbsT * D * 4 + (size_t)4 * kAbsT * 64 * 4;
@@ -488,6 +496,11 @@ size_t ggb_latent_attn_scratch_bytes(int64_t T, int H, int R, int n_split) {
 
 int ggb_op_latent_attn(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
                        int64_t T, int H, int R, int Dr, int n_split, float *part) {
+    return ggb_op_latent_attn_window(dt, qa, cache, block_table, block_size, pos0, T, H, R, Dr, 0, n_split, part);
+}
+
+int ggb_op_latent_attn_window(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
+                              int64_t T, int H, int R, int Dr, int64_t window, int n_split, float *part) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(qa && cache && block_table && pos0 && part && T > 0 && H > 0 && R > 0 && R <= 1024 && Dr >= 0 && n_split > 0 &&
@@ -495,15 +508,21 @@ int ggb_op_latent_attn(int dt, const float *qa, const void *cache, const int32_t
                   "latent_attn: bad arguments (latent size up to 1024)");
     const int64_t ldk = ggb_latent_cache_ld(R, Dr);
     if (dt == GGB_TYPE_BF16)
-        return attn_partial_launch<__nv_bfloat16>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, part);
-    return attn_partial_launch<float>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, part);
+        return attn_partial_launch<__nv_bfloat16>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, window, part);
+    return attn_partial_launch<float>(qa, cache, ldk, block_table, block_size, pos0, T, H, R, Dr, n_split, window, part);
 }
 
 int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
                            void *out) {
+    GGB_CHECK_ARG(sink != nullptr, "latent_attn_out: no sink");
+    return ggb_op_latent_attn_out_gated(dt, part, n_split, sink, w_uv, T, H, R, Dv, nullptr, 0, out);
+}
+
+int ggb_op_latent_attn_out_gated(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
+                                 const float *gate, int64_t ldg, void *out) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(part && sink && w_uv && out && T > 0 && H > 0 && R > 0 && Dv > 0 && n_split > 0, "latent_attn_out: bad arguments");
+    GGB_CHECK_ARG((!gate || ldg >= H) && part && w_uv && out && T > 0 && H > 0 && R > 0 && Dv > 0 && n_split > 0, "latent_attn_out: bad arguments");
     // few tokens: spread a head's outputs over several CTAs; many tokens: the grid is large already, merge once per head
     const int v_chunk = T * H >= 1024 ? Dv : 16;
     const dim3 grid((unsigned)((T + kOutT - 1) / kOutT), (unsigned)H, (unsigned)((Dv + v_chunk - 1) / v_chunk));
@@ -511,9 +530,9 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
     GGB_CHECK_ARG(smem <= 48 * 1024, "latent_attn_out: latent size %d with %d splits too large", R, n_split);
     if (dt == GGB_TYPE_BF16)
         latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const __nv_bfloat16 *)w_uv, T, H, R, Dv,
-                                                                       v_chunk, (__nv_bfloat16 *)out);
+                                                                       v_chunk, gate, ldg, (__nv_bfloat16 *)out);
     else
-        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const float *)w_uv, T, H, R, Dv, v_chunk, (float *)out);
+        latent_attn_out_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(part, n_split, sink, (const float *)w_uv, T, H, R, Dv, v_chunk, gate, ldg, (float *)out);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

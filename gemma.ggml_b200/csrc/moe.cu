@@ -77,6 +77,64 @@ __global__ void __launch_bounds__(32) moe_select_kernel(const float *__restrict_
     }
 }
 
+// one warp per token, sigmoid scores with a choice correction and groups: s = sigmoid(z); the choice score of expert e is
+// s_e + corr_e; the experts form n_groups equal groups of neighbours, a group's score is the sum of its two largest
+// choice scores, and only experts of the `keep` best groups (ties: the lower group) can be chosen; among them the `top`
+// largest choice scores win (ties: the lower index).  The weight of a chosen expert is its plain s, not renormalised.
+__global__ void __launch_bounds__(32) moe_select_sigmoid_kernel(const float *__restrict__ zg, const float *__restrict__ corr, int n_exp, int top,
+                                                                int n_groups, int keep, int32_t *__restrict__ idx, float *__restrict__ wt) {
+    extern __shared__ float sm[]; // [n_exp] scores, [n_exp] choice scores, [n_groups] group scores
+    float *sc = sm, *ch = sm + n_exp, *gsc = ch + n_exp;
+    const int64_t t = blockIdx.x;
+    const int lane = threadIdx.x, gs = n_exp / n_groups;
+    for (int e = lane; e < n_exp; e += 32) {
+        const float s = 1.0f / (1.0f + expf(-zg[t * n_exp + e]));
+        sc[e] = s;
+        ch[e] = s + (corr ? corr[e] : 0.f);
+    }
+    __syncwarp();
+    if (keep < n_groups) {
+        for (int g = lane; g < n_groups; g += 32) { // the two largest of the group, in index order
+            float a = -INFINITY, b = -INFINITY;
+            for (int e = g * gs; e < (g + 1) * gs; e++) {
+                const float v = ch[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gsc[g] = gs > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // a group stays when fewer than `keep` groups come before it in the order (larger score, then lower index)
+        for (int g = lane; g < n_groups; g += 32) {
+            int before = 0;
+            for (int o = 0; o < n_groups; o++) before += (gsc[o] > gsc[g]) || (gsc[o] == gsc[g] && o < g);
+            if (before >= keep)
+                for (int e = g * gs; e < (g + 1) * gs; e++) ch[e] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int k = 0; k < top; k++) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int e = lane; e < n_exp; e += 32) {
+            const float v = ch[e];
+            if (!isnan(sc[e]) && sc[e] >= 0.f && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            idx[t * top + k] = bi;
+            wt[t * top + k] = sc[bi];
+            sc[bi] = -1.0f; // taken: a score is never negative otherwise
+        }
+        __syncwarp();
+    }
+}
+
 // one CTA: counts per expert, offsets, the list of 64-row tiles, and the sorted order of the n = T * top slots
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ idx, int n, int top, int n_exp, int32_t *offsets,
                                                          int32_t *row_src, int32_t *inv, int32_t *tile_expert, int32_t *tile_row0,
@@ -179,6 +237,25 @@ int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w
         moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const float *)h, W, T, w_router, bias, n_exp, logits);
     GGB_LAUNCH_CHECK();
     moe_select_kernel<<<(unsigned)T, 32, smem, ggb_cuda_stream()>>>(logits, n_exp, top, idx, wt);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_moe_route_sigmoid(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *correction, int n_exp, int top,
+                             int n_groups, int keep, float *logits, int32_t *idx, float *wt) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(h && w_router && idx && wt && logits && W > 0 && T > 0 && n_exp > 0 && top > 0 && n_exp <= 4096, "moe_route_sigmoid: bad arguments");
+    GGB_CHECK_ARG(n_groups > 0 && n_exp % n_groups == 0 && keep > 0 && keep <= n_groups && top <= keep * (n_exp / n_groups),
+                  "moe_route_sigmoid: %d experts in %d groups of which %d stay cannot give %d experts", n_exp, n_groups, keep, top);
+    const unsigned blocks = (unsigned)((T * n_exp + 7) / 8);
+    if (dt == GGB_TYPE_BF16)
+        moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, T, w_router, nullptr, n_exp, logits);
+    else
+        moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const float *)h, W, T, w_router, nullptr, n_exp, logits);
+    GGB_LAUNCH_CHECK();
+    moe_select_sigmoid_kernel<<<(unsigned)T, 32, (size_t)(2 * n_exp + n_groups) * 4, ggb_cuda_stream()>>>(logits, correction, n_exp, top, n_groups,
+                                                                                                         keep, idx, wt);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

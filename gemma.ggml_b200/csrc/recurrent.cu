@@ -27,10 +27,11 @@ constexpr int kConvMaxTaps = 8, kConvTokens = 32;
 // it.  Chunk 0 is the only reader of the old tail and its only writer (after it has the old values in registers).
 template <typename E>
 __global__ void __launch_bounds__(128) causal_conv_kernel(const float *__restrict__ x, int64_t ldx, int64_t T, int64_t C,
-                                                          const float *__restrict__ w, int taps, int add_input, int act, float *tail,
-                                                          float *__restrict__ y_f32, int64_t ldy, E *__restrict__ y_dt) {
+                                                          const float *__restrict__ w, const float *__restrict__ bias, int taps, int add_input,
+                                                          int act, float *tail, float *__restrict__ y_f32, int64_t ldy, E *__restrict__ y_dt) {
     const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
+    const float xb = bias ? bias[c] : 0.f; // the input is x + bias; the tail keeps it so
     const int64_t t0 = (int64_t)blockIdx.y * kConvTokens, t1 = min(T, t0 + kConvTokens);
     const int nt = taps - 1;
     float wt[kConvMaxTaps], win[kConvMaxTaps], old[kConvMaxTaps];
@@ -49,10 +50,10 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float *__restric
     for (int j = 0; j < kConvMaxTaps - 1; j++)
         if (j < nt) {
             const int64_t s = t0 - nt + j;
-            win[j] = s >= 0 ? x[s * ldx + c] : old[j]; // s < 0 only in chunk 0, where s + nt = j indexes the old tail
+            win[j] = s >= 0 ? x[s * ldx + c] + xb : old[j]; // s < 0 only in chunk 0, where s + nt = j indexes the old tail
         }
     for (int64_t t = t0; t < t1; t++) {
-        const float xv = x[t * ldx + c];
+        const float xv = x[t * ldx + c] + xb;
         float acc = 0.f;
 #pragma unroll
         for (int j = 0; j < kConvMaxTaps - 1; j++)
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float *__restric
             if (j < nt) {
                 const int64_t s = T - nt + j;
                 float v = 0.f;
-                if (s >= 0) v = x[s * ldx + c];
+                if (s >= 0) v = x[s * ldx + c] + xb;
                 else {
 #pragma unroll
                     for (int i = 0; i < kConvMaxTaps - 1; i++)
@@ -310,6 +311,11 @@ extern "C" {
 
 int ggb_op_causal_conv(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, int taps, int add_input, int act,
                        float *tail, float *y_f32, int64_t ldy, void *y_dt) {
+    return ggb_op_causal_conv_bias(dt, x, ldx, T, C, w, nullptr, taps, add_input, act, tail, y_f32, ldy, y_dt);
+}
+
+int ggb_op_causal_conv_bias(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, const float *bias, int taps,
+                            int add_input, int act, float *tail, float *y_f32, int64_t ldy, void *y_dt) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "causal_conv: dtype %d is neither bf16 nor f32", dt);
     GGB_CHECK_ARG(x && w && T > 0 && C > 0 && ldx >= C && taps >= 1 && taps <= kConvMaxTaps && (taps == 1 || tail) && (y_f32 || y_dt) &&
@@ -317,9 +323,9 @@ int ggb_op_causal_conv(int dt, const float *x, int64_t ldx, int64_t T, int64_t C
                   "causal_conv: bad arguments (taps %d, at most %d)", taps, kConvMaxTaps);
     const dim3 grid((unsigned)((C + 127) / 128), (unsigned)((T + kConvTokens - 1) / kConvTokens));
     if (dt == GGB_TYPE_BF16)
-        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, taps, add_input, act, tail, y_f32, ldy, (__nv_bfloat16 *)y_dt);
+        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, bias, taps, add_input, act, tail, y_f32, ldy, (__nv_bfloat16 *)y_dt);
     else
-        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, taps, add_input, act, tail, y_f32, ldy, (float *)y_dt);
+        causal_conv_kernel<<<grid, 128, 0, ggb_cuda_stream()>>>(x, ldx, T, C, w, bias, taps, add_input, act, tail, y_f32, ldy, (float *)y_dt);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

@@ -1,6 +1,7 @@
 // capi.cpp — flat C entry points over gemma_model so tests / bench.py can drive the host side with
 // ctypes (the reference drives its model from app::run, ref: src/app.cpp:30-44).
 #include <cstdio>
+#include <algorithm>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -9,6 +10,7 @@
 #include "gguf_loader.h"
 #include "lm_engine.h"
 #include "begupel_model.h"
+#include "ditalorn_model.h"
 #include "safolorn_model.h"
 #include "tensor_dump.h"
 
@@ -216,6 +218,26 @@ int bg_config_probe(const char *text, int64_t *out) {
     int64_t win = 0;
     for (const auto &l : c.layers) win += l.type == 1;
     out[0] = (int64_t)c.layers.size(); out[1] = win; out[2] = c.vocab; out[3] = c.width; out[4] = c.groups; out[5] = c.taps;
+    return 0;
+}
+// host only: parses a Ditalorn configuration text; out[8] = {layers, attention layers, latent layers, layers with experts,
+// vocab, width, positions, widest window (0: some layer sees everything)}; -1 and gm_last_error() when it is refused
+int dl_config_probe(const char *text, int64_t *out) {
+    json_value j;
+    dl_config c;
+    if (!json_parser(text, strlen(text)).parse(&j, &g_capi_err)) return -1;
+    if (dl_parse_config(j, nullptr, &c, &g_capi_err)) return -1;
+    int64_t attn = 0, lat = 0, moe = 0, win = 0;
+    bool bounded = true;
+    for (const auto &l : c.layers) {
+        attn += l.type == 0;
+        lat += l.type == 1;
+        moe += l.moe.experts > 0;
+        if (l.type == 0 || l.latent.window <= 0) bounded = false;
+        else win = std::max<int64_t>(win, l.latent.window);
+    }
+    out[0] = (int64_t)c.layers.size(); out[1] = attn; out[2] = lat; out[3] = moe; out[4] = c.vocab; out[5] = c.width;
+    out[6] = c.max_positions; out[7] = bounded ? win : 0;
     return 0;
 }
 // host only: a tensor of a .safetensors file: returns its number of dimensions (shape[0 .. 8) filled, *nbytes, dtype text),

@@ -289,6 +289,14 @@ int ggb_op_softcap(float *x, int64_t n, float cap);
  * act(gate) with gate fp32 rows of stride ldg; act 0: sigmoid, 1: silu; y in dt, dense [T][n_groups * gs] */
 int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int64_t ldg, int64_t T, int n_groups, int gs, const float *w,
                      int w_period, float eps, int act, void *y);
+/* token embedding with learned positions: y[t] = table[ids[t]] * scale + pos_table[*pos0 + t] (pos_table may be NULL) */
+int ggb_op_embed_pos(int dt, const void *table, const void *pos_table, const int32_t *ids, const int32_t *pos0, int64_t T, int64_t E,
+                     float scale, float *y);
+/* norms on both sides of a sublayer in one pass over the row: v = a (+ bias); x += v / sqrt(mean(v^2) + eps) * wa; then,
+ * with y, y (dt) = x / sqrt(mean(x^2) + eps) * wy: the input of the next sublayer.  Weights as they multiply (a weight
+ * stored around zero is handed in as 1 + w). */
+int ggb_op_norm_add_norm(int dt, const float *a, const float *bias, const float *wa, float eps, int64_t E, int64_t T, float *x,
+                         const float *wy, void *y);
 
 /* ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
  * State that a sequence carries from token to token (fp32, one block per sequence, handed in by the caller): tails of
@@ -300,6 +308,9 @@ int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int
  * [(taps - 1)][C] is replaced by the last taps - 1 inputs.  taps <= 8. */
 int ggb_op_causal_conv(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, int taps, int add_input, int act,
                        float *tail, float *y_f32, int64_t ldy, void *y_dt);
+/* the same on the input x + bias[c] (a projection's bias added on the way in; the tail keeps the biased values; bias may be NULL) */
+int ggb_op_causal_conv_bias(int dt, const float *x, int64_t ldx, int64_t T, int64_t C, const float *w, const float *bias, int taps,
+                            int add_input, int act, float *tail, float *y_f32, int64_t ldy, void *y_dt);
 /* lightning attention: q, k [T][H * D], v [T][H * Dv] raw projections (row stride ld); per head with q = silu(q),
  * k = silu(k), v = silu(v): S <- decay[h] S + k v^T, o = S^T q.  state [H][D][Dv] in / out, o fp32 [T][H * Dv]. */
 int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int D, int Dv, const float *decay,
@@ -332,6 +343,25 @@ size_t ggb_window_attn_scratch_bytes(int H);
 int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
                        int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out, float *scratch);
 
+/* ------------------------------------------------------------------ sigmoid attention (csrc/sigmoid_attention.cu)
+ * Grouped-query attention with unnormalised weights over the same paged rows [k (G * D) | v (G * Dv)] (ggb_window_cache_ld):
+ * the weight of key j for the query at position i is sigmoid(q . k - r1[h] ln(1 + r2[h] (i - j)) + pb[h]), the output
+ * the plain weighted sum of the values.
+ *
+ * qkv_store: q [T][H * D], k [T][G * D], v [T][G * Dv] fp32 (row stride ld).  q times its temperature
+ * 1 + temp_coef ln(floor((p + 1) / temp_every) + 1) at position p (temp_every 0: none) times scale -> q_out fp32
+ * [T][H * D]; k and every value head divided by its root mean square (vnorm_eps < 0: as it is) -> the cache row. */
+int ggb_op_sigmoid_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
+                             float temp_coef, int temp_every, float vnorm_eps, float scale, const int32_t *pos0, const int32_t *block_table,
+                             int block_size, void *cache, float *q_out);
+/* token t at position i = *pos0 + t sees j <= i (window > 0: 0 <= i - j < window); r1 / r2 (both or neither) and pb are
+ * per-head fp32 and may be NULL; out (dt) [T][H * Dv].  scratch (ggb_sigmoid_attn_scratch_bytes, may be NULL): lets a
+ * step of few tokens spread a (token, head)'s keys over several CTAs */
+size_t ggb_sigmoid_attn_scratch_bytes(int H);
+int ggb_op_sigmoid_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
+                        int H, int G, int D, int Dv, int64_t window, const float *r1, const float *r2, const float *pb, void *out,
+                        float *scratch);
+
 /* ------------------------------------------------------------------ latent attention (csrc/latent_attention.cu)
  * The cache of a layer holds one row [c (R) | kr (Dr)] per position, ggb_latent_cache_ld(R, Dr) numbers apart, in pages
  * of block_size positions: position j is row block_table[j / block_size] * block_size + j %% block_size.  The step's
@@ -353,6 +383,14 @@ int ggb_op_latent_attn(int dt, const float *qa, const void *cache, const int32_t
  * out[t][h * Dv ..] (dt) = w_uv_h (sum_j p_j c_j) */
 int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
                            void *out);
+/* the same over a sliding window: the token at position i sees the keys j with 0 <= i - j < window (window <= 0: every
+ * j <= i); the splits deal the tiles from the first visible one */
+int ggb_op_latent_attn_window(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
+                              int64_t T, int H, int R, int Dr, int64_t window, int n_split, float *part);
+/* the merge without a sink (sink NULL: ordinary soft-max over the keys) and / or with an output gate: head h of token t
+ * is multiplied by sigmoid(gate[t * ldg + h]) (fp32 raw projections; gate NULL: none) */
+int ggb_op_latent_attn_out_gated(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
+                                 const float *gate, int64_t ldg, void *out);
 
 /* ------------------------------------------------------------------ mixture of experts (csrc/moe.cu)
  * route: fp32 logits w_router h + bias, the `top` largest (ties: lower index), weights = soft-max over the chosen.
@@ -361,6 +399,12 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
  * row; act 1: c = relu(.)^2 in dt, act 0: c fp32.  combine: out[t] = sum_s wt[t][s] y[sorted row of slot s]. */
 int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *bias, int n_exp, int top,
                      float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt);
+/* route with sigmoid scores: s = sigmoid(w_router h) in fp32; the choice score of an expert is s + correction (may be
+ * NULL); the experts form n_groups equal groups of neighbours, a group's score is the sum of its two largest choice
+ * scores, and only the `keep` best groups can be chosen from (ties: the lower index, for groups and experts); the `top`
+ * largest choice scores win and the weights are their s, not renormalised */
+int ggb_op_moe_route_sigmoid(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *correction, int n_exp, int top,
+                             int n_groups, int keep, float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt);
 int ggb_moe_max_tiles(int64_t n_slots, int n_exp);
 size_t ggb_moe_group_ints(int64_t n_slots, int n_exp);
 int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t *ws);
