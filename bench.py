@@ -885,12 +885,118 @@ def run_begupel(args):
                       "peaks": peaks, "sizes": records}), flush=True)
 
 
+DITALORN_SIZES = {  # width, layers, heads, kv_heads, dim, q_rank, kv_rank, window, experts, top, groups, keep, expert ff, vocab
+    "s": (1024, 8, 8, 2, 128, 384, 256, 1024, 16, 2, 4, 2, 1024, 32000),
+    "m": (2048, 8, 16, 4, 128, 768, 512, 1024, 32, 4, 8, 4, 1408, 32000),
+    "l": (4096, 4, 32, 8, 128, 1536, 512, 2048, 16, 2, 4, 2, 2048, 32000),
+}
+DL_OPS = ("op_linear", "op_sigmoid_attn", "op_attn", "op_attn_prep", "op_attn_out", "op_conv", "op_moe", "op_moe_linear", "op_norm", "op_act",
+          "op_residual", "op_rows")
+
+
+def ditalorn_config(size, positions):
+    """Layers alternate: sigmoid attention over every earlier position, then latent attention over a window; experts everywhere."""
+    W, L, H, Gk, D, Rq, R, win, E, top, groups, keep, eff, V = DITALORN_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top, "groups": {"count": groups, "keep": keep}}}
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            mx = {"heads": H, "kv_heads": Gk, "dim": D, "vdim": D, "conv": 4, "scale": D ** -0.5, "q_temp": {"coef": 0.1, "every": 256}}
+            layers.append({"type": "attention", "mixer": mx, "mlp": mlp})
+        else:
+            mx = {"heads": H, "dim": D, "vdim": D, "q_rank": Rq, "kv_rank": R, "scale": D ** -0.5, "mask": {"size": win}}
+            layers.append({"type": "latent_attention", "mixer": mx, "mlp": mlp})
+    return {"architecture": "Ditalorn", "vocab": V, "width": W, "max_positions": positions, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0}, "layers": layers}
+
+
+def run_ditalorn(args):
+    """--arch ditalorn: prefill and decode throughput of the Ditalorn design (random bf16 weights) at layer sizes of real
+    models, through the serving engine (host call: H2D token ids, operator launches / graph replay, D2H result), with
+    cudaEvent time per operator class and roofline fractions; beside it Safolorn, the closest model of the framework (latent
+    attention and experts through the same operators), at the same width, depth, heads, latent and expert sizes."""
+    import gemma_ggml_b200 as G
+    G.init(0)
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks = {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops_sustained": float(pk["bf16_tflops_sustained"]), "source": "MEASURED_PEAKS.json"}
+    except Exception:
+        pass
+    T, ctx, n_dec = args.prefill_tokens if args.prefill_tokens != 512 else 2048, args.ctx, min(args.steps, 128)
+    records = {}
+    for size in args.sizes.split(","):
+        W, nl, H, Gk, D, Rq, R, win, E, top, groups, keep, eff, V = DITALORN_SIZES[size]
+        cfg = ditalorn_config(size, ctx + n_dec + 64)
+        eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+        pf, pf_ops, dec, dc_ops, kernels, clocks = _engine_times(G, eng, V, T, ctx, n_dec, DL_OPS)
+        wbytes = eng.stats()["weight_bytes"]
+        eng.close()
+        n_att, n_lat = (nl + 1) // 2, nl // 2
+        vis_all = T * (T + 1) / 2.0
+        vis_win = float(sum(min(i + 1, win) for i in range(T)))
+        lin_params = n_att * (W * (H * D + 2 * Gk * D) + W * H * D) + n_lat * (W * (Rq + R + H) + Rq * H * D + W * H * D)
+        lin_flops, lin_bytes = 2.0 * T * lin_params + 2.0 * V * W, 2.0 * (lin_params + V * W)
+        sig_flops = 4.0 * n_att * H * D * vis_all                # q.k and p.v
+        lat_flops = 4.0 * n_lat * H * R * vis_win                # the absorbed form: qa.c and p.c, R numbers each
+        moe_flops = 2.0 * T * top * 3 * eff * W * nl
+        moe_bytes = 2.0 * top * 3 * eff * W * nl
+        sig_cache, lat_cache = 2.0 * n_att * ctx * 2 * Gk * D, 2.0 * n_lat * min(ctx, win) * R
+        rec = {
+            "config": {"width": W, "layers": nl, "heads": H, "kv_heads": Gk, "dim": D, "q_rank": Rq, "kv_rank": R, "window": win, "experts": E, "top": top,
+                       "groups": [groups, keep], "expert_ff": eff, "vocab": V, "weight_bytes": wbytes},
+            "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks,
+                        "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
+                        "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                        "moe_linear_tflops": moe_flops / (pf_ops["op_moe_linear"] / 1e3) / 1e12,
+                        "sigmoid_attn_tflops_cuda_cores": sig_flops / (pf_ops["op_sigmoid_attn"] / 1e3) / 1e12,
+                        "latent_attn_tflops_cuda_cores": lat_flops / (pf_ops["op_attn"] / 1e3) / 1e12},
+            "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
+                       "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                       "moe_linear_gbs": moe_bytes / (dc_ops["op_moe_linear"] / 1e3) / 1e9,
+                       "sigmoid_attn_gbs": sig_cache / (dc_ops["op_sigmoid_attn"] / 1e3) / 1e9, "latent_attn_gbs": lat_cache / (dc_ops["op_attn"] / 1e3) / 1e9,
+                       "token_frac_of_hbm_roofline": ((lin_bytes + moe_bytes + sig_cache + lat_cache) / (peaks["hbm_gbs"] * 1e9)) / dec},
+        }
+        if not args.no_sub_records:  # Safolorn at equal size: latent attention in every layer, the same experts
+            mx = {"heads": H, "dim": D, "rot_dim": 64, "vdim": D, "kv_rank": R, "scale": (D + 64) ** -0.5,
+                  "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            scfg = {"architecture": "Safolorn", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+                    "layers": [{"type": "latent_attention", "mixer": mx, "mlp": {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}}} for _ in range(nl)]}
+            seng = G.Engine(config=scfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+            spf, spf_ops, sdec, sdc_ops, skernels, _ = _engine_times(G, seng, V, T, ctx, n_dec, DL_OPS)
+            s_params = nl * (W * (H * (D + 64) + R + 64) + W * H * D)
+            s_flops, s_bytes = 2.0 * T * s_params + 2.0 * V * W, 2.0 * (s_params + V * W)
+            s_attn = 2.0 * nl * H * (2 * R + 64) * vis_all
+            s_moe_flops, s_moe_bytes = 2.0 * T * top * 2 * eff * W * nl, 2.0 * top * 2 * eff * W * nl  # experts without a gate: up and down
+            s_cache = 2.0 * nl * ctx * (R + 64)
+            rec["safolorn_equal_size"] = {
+                "config": {"weight_bytes": seng.stats()["weight_bytes"]},
+                "prefill": {"tokens_per_s": T / spf, "ms": 1e3 * spf, "op_ms": spf_ops, "linear_tflops": s_flops / (spf_ops["op_linear"] / 1e3) / 1e12,
+                            "linear_frac_of_tensor_peak": s_flops / (spf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                            "moe_linear_tflops": s_moe_flops / (spf_ops["op_moe_linear"] / 1e3) / 1e12,
+                            "latent_attn_tflops_cuda_cores": s_attn / (spf_ops["op_attn"] / 1e3) / 1e12},
+                "decode": {"tokens_per_s": 1.0 / sdec, "us_per_token": 1e6 * sdec, "kernels_per_token": skernels, "op_us": {k: 1e3 * v for k, v in sdc_ops.items()},
+                           "linear_gbs": s_bytes / (sdc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": s_bytes / (sdc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                           "moe_linear_gbs": s_moe_bytes / (sdc_ops["op_moe_linear"] / 1e3) / 1e9,
+                           "latent_attn_gbs": s_cache / (sdc_ops["op_attn"] / 1e3) / 1e9,
+                           "token_frac_of_hbm_roofline": ((s_bytes + s_moe_bytes + s_cache) / (peaks["hbm_gbs"] * 1e9)) / sdec},
+            }
+            seng.close()
+        records[size] = rec
+    first = records[args.sizes.split(",")[0]]
+    print(json.dumps({"metric": "ditalorn decode tokens/s", "value": first["decode"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": n_dec, "warmup": 8, "ms_per_step": first["decode"]["us_per_token"] / 1e3, "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random bf16 weights of the configured sizes)",
+                      "config": {"workload": "Ditalorn sizes " + args.sizes + ": prefill of %d tokens, greedy decode at n_kv %d, through the serving engine" % (T, ctx),
+                                 "l2": "weights of every size exceed the 126 MB L2"},
+                      "peaks": peaks, "sizes": records}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn", "begupel"],
+    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn", "begupel", "ditalorn"],
                     help="gemma: the headline workload (default); safolorn: throughput of the Safolorn design beside Gemma at equal size; "
-                         "begupel: throughput of the Begupel design beside Safolorn at equal size")
-    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn / begupel: which of the sizes s, m, l to run")
+                         "begupel: throughput of the Begupel design beside Safolorn at equal size; ditalorn: the Ditalorn design beside Safolorn at equal size")
+    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn / begupel / ditalorn: which of the sizes s, m, l to run")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
@@ -912,6 +1018,8 @@ def main():
         run_safolorn(args)
     elif args.arch == "begupel":
         run_begupel(args)
+    elif args.arch == "ditalorn":
+        run_ditalorn(args)
     elif args.mode == "prefill":
         run_prefill(args)
     else:

@@ -420,7 +420,7 @@ int ditalorn_model::emit(int T, int ns, const int32_t *table, float *state, int 
                                                      nullptr));
             DL_OP("op_attn_prep", ggb_op_sigmoid_qkv_store(dt_, cv_, cv_ + HD, cv_ + HD + GD, C, t, A.heads, A.kv_heads, A.dim, A.vdim, A.temp_coef,
                                                            A.temp_every, c.eps, A.scale, pos0_, table, B, cache, q_));
-            DL_OP("op_attn", ggb_op_sigmoid_attn(dt_, q_, cache, table, B, pos0_, t, A.heads, A.kv_heads, A.dim, A.vdim, 0, w.r1, w.r2, w.pb, ao_, sa_));
+            DL_OP("op_sigmoid_attn", ggb_op_sigmoid_attn(dt_, q_, cache, table, B, pos0_, t, A.heads, A.kv_heads, A.dim, A.vdim, 0, w.r1, w.r2, w.pb, ao_, sa_));
             DL_OP("op_linear", ggb_op_linear(dt_, w.o, W, (int64_t)A.heads * A.vdim, ao_, (int64_t)A.heads * A.vdim, t, ya_, W));
             mixer_bias = w.o_b;
         } else {
