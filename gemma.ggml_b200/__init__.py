@@ -157,8 +157,10 @@ _CUDA_SIG = {
     "ggb_op_moe_group": (i32, [vp, i64, i32, i32, vp]),
     "ggb_op_moe_linear": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, vp, i32, vp, i64]),
     "ggb_op_moe_combine": (i32, [vp, vp, vp, i64, i32, i32, i64, vp]),
-    "ggb_op_moe_route_sigmoid": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, i32, i32, vp, vp, vp]),
-    "ggb_op_embed_pos": (i32, [i32, vp, vp, vp, vp, i64, i64, f32, vp]),
+    "ggb_op_moe_route_sigmoid": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp]),
+    "ggb_moe_step_form": (i32, [i64]),
+    "ggb_op_moe_combine_norm": (i32, [i32, vp, vp, vp, i64, i32, i32, i64, vp, f32, vp, vp, vp]),
+    "ggb_op_embed_pos": (i32, [i32, vp, vp, vp, vp, i64, i64, f32, vp, vp, f32, vp]),
     "ggb_op_norm_add_norm": (i32, [i32, vp, vp, vp, f32, i64, i64, vp, vp, vp]),
     "ggb_op_causal_conv_bias": (i32, [i32, vp, i64, i64, i64, vp, vp, i32, i32, i32, vp, vp, i64, vp]),
     "ggb_op_latent_attn_window": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i64, i32, vp]),

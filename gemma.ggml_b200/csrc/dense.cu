@@ -648,28 +648,57 @@ namespace {
 // one CTA per token: the embedding row times `scale` plus the (unscaled) row of the token's position
 template <typename E>
 __global__ void __launch_bounds__(256) embed_pos_kernel(const E *__restrict__ table, const E *__restrict__ pos_table, const int32_t *__restrict__ ids,
-                                                        const int32_t *__restrict__ pos0, int64_t n, float scale, float *__restrict__ y) {
+                                                        const int32_t *__restrict__ pos0, int64_t n, float scale, float *__restrict__ y,
+                                                        const float *__restrict__ wn, float eps, E *__restrict__ yn) {
+    __shared__ float red[8];
     const int64_t t = blockIdx.x;
     const E *e = table + (int64_t)ids[t] * n;
     const E *p = pos_table ? pos_table + ((int64_t)*pos0 + t) * n : nullptr;
+    float ss = 0.f;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = to_f32(e[i]) * scale;
-        y[t * n + i] = p ? v + to_f32(p[i]) : v;
+        float v = to_f32(e[i]) * scale;
+        if (p) v += to_f32(p[i]);
+        y[t * n + i] = v;
+        ss = fmaf(v, v, ss);
     }
+    if (!yn) return;
+    // the first layer's norm on the way out: a thread reads back what it wrote itself
+    const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)n + eps);
+    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) yn[t * n + i] = from_f32<E>(y[t * n + i] * r * wn[i]);
 }
 
 // one CTA per token: x += (a + bias) / rms(a + bias) * wa, then y = x / rms(x) * wy.  The row stays in shared memory
 // between the passes; both root mean squares and the sum are fp32.
+constexpr int kMaxCombine = GGB_MOE_COMBINE_NORM_MAX_TOP;
+// With inv / wt the sublayer's output is gathered on the way in: v = sum_k wt[t][k] a[inv[t][k]] over the `top` expert
+// slots of the token, added in slot order (what moe_combine_kernel computes).
 template <typename E>
 __global__ void __launch_bounds__(256) norm_add_norm_kernel(const float *__restrict__ a, const float *__restrict__ bias,
+                                                            const int32_t *__restrict__ inv, const float *__restrict__ wt, int top,
                                                             const float *__restrict__ wa, float eps, int64_t n, float *x,
                                                             const float *__restrict__ wy, E *__restrict__ y) {
     extern __shared__ float nn_row[];
     __shared__ float red[8];
+    __shared__ float s_wt[kMaxCombine];
+    __shared__ int64_t s_off[kMaxCombine];
     const int64_t t = blockIdx.x;
+    if (inv) { // the token's slots, looked up once: the loads below then depend on nothing
+        if ((int)threadIdx.x < top) {
+            s_wt[threadIdx.x] = wt[t * top + threadIdx.x];
+            s_off[threadIdx.x] = (int64_t)inv[t * top + threadIdx.x] * n;
+        }
+        __syncthreads();
+    }
     float ss = 0.f;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = a[t * n + i];
+        float v;
+        if (inv) {
+            v = 0.f;
+#pragma unroll 4
+            for (int k = 0; k < top; k++) v = fmaf(s_wt[k], a[s_off[k] + i], v);
+        } else {
+            v = a[t * n + i];
+        }
         if (bias) v += bias[i];
         nn_row[i] = v;
         ss = fmaf(v, v, ss);
@@ -692,36 +721,42 @@ __global__ void __launch_bounds__(256) norm_add_norm_kernel(const float *__restr
 extern "C" {
 
 int ggb_op_embed_pos(int dt, const void *table, const void *pos_table, const int32_t *ids, const int32_t *pos0, int64_t T, int64_t E,
-                     float scale, float *y) {
+                     float scale, float *y, const float *wn, float eps, void *yn) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(table && ids && y && T > 0 && E > 0 && (!pos_table || pos0), "embed_pos: bad arguments");
+    GGB_CHECK_ARG(table && ids && y && T > 0 && E > 0 && (!pos_table || pos0) && (!yn || wn), "embed_pos: bad arguments");
     if (dt == GGB_TYPE_BF16)
         embed_pos_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)table, (const __nv_bfloat16 *)pos_table, ids, pos0, E,
-                                                                     scale, y);
+                                                                     scale, y, wn, eps, (__nv_bfloat16 *)yn);
     else
-        embed_pos_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const float *)table, (const float *)pos_table, ids, pos0, E, scale, y);
+        embed_pos_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>((const float *)table, (const float *)pos_table, ids, pos0, E, scale, y, wn, eps,
+                                                                     (float *)yn);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }
 
 int ggb_op_norm_add_norm(int dt, const float *a, const float *bias, const float *wa, float eps, int64_t E, int64_t T, float *x,
                          const float *wy, void *y) {
+    return ggb_norm_add_norm_launch(dt, a, bias, nullptr, nullptr, 0, wa, eps, E, T, x, wy, y);
+}
+
+} // extern "C"
+
+int ggb_norm_add_norm_launch(int dt, const float *a, const float *bias, const int32_t *inv, const float *wt, int top, const float *wa, float eps,
+                             int64_t E, int64_t T, float *x, const float *wy, void *y) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(a && wa && x && E > 0 && T > 0 && (!y || wy), "norm_add_norm: bad arguments");
+    GGB_CHECK_ARG(a && wa && x && E > 0 && T > 0 && (!y || wy) && (!inv || (wt && top > 0 && top <= kMaxCombine)), "norm_add_norm: bad arguments");
     const size_t smem = (size_t)E * 4;
     GGB_CHECK_ARG(smem <= 200 * 1024, "norm_add_norm: width %lld does not fit shared memory", (long long)E);
 #define NN_LAUNCH(ET)                                                                                                         \
     {                                                                                                                          \
         auto k = norm_add_norm_kernel<ET>;                                                                                     \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
-        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(a, bias, wa, eps, E, x, wy, (ET *)y);                                  \
+        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(a, bias, inv, wt, top, wa, eps, E, x, wy, (ET *)y);                                  \
     }
     if (dt == GGB_TYPE_BF16) NN_LAUNCH(__nv_bfloat16) else NN_LAUNCH(float)
 #undef NN_LAUNCH
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }
-
-} // extern "C"

@@ -29,6 +29,11 @@ bool ggb_gemm_grouped_bf16_fits(int64_t N, int64_t K, int64_t ldc);
 int ggb_gemm_grouped_bf16(const void *w, int64_t N, int64_t K, const void *a, int64_t n_rows, int n_exp, const int32_t *offsets, float *c,
                           void *c_act, int64_t ldc);
 
+// norms on both sides of a sublayer (ggb_op_norm_add_norm); with inv / wt the sublayer's output is the weighted sum of
+// the token's `top` expert slots, gathered on the way in (moe.cu)
+int ggb_norm_add_norm_launch(int dt, const float *a, const float *bias, const int32_t *inv, const float *wt, int top, const float *wa, float eps,
+                             int64_t E, int64_t T, float *x, const float *wy, void *y);
+
 #ifdef __CUDACC__
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -3,6 +3,8 @@
 // weighted sum.  A token's result does not depend on which other tokens share the step: every slot is computed by
 // itself in k order and the `top` slot outputs are added in slot order.
 #include <cuda_bf16.h>
+
+#include <algorithm>
 #include <math.h>
 
 #include "common.cuh"
@@ -10,17 +12,9 @@
 
 namespace {
 
-// router logits: a warp per (token, expert), z[t][e] = w[e] . h[t] + b[e] in fp32
+// one warp: w . h in fp32, the same order of sums wherever it is called from
 template <typename E>
-__global__ void __launch_bounds__(256) moe_logits_kernel(const E *__restrict__ h, int64_t W, int64_t T, const float *__restrict__ w,
-                                                         const float *__restrict__ b, int n_exp, float *__restrict__ z) {
-    const int lane = threadIdx.x & 31;
-    const int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (i >= T * n_exp) return;
-    const int64_t t = i / n_exp;
-    const int e = (int)(i - t * n_exp);
-    const E *hr = h + t * W;
-    const float *wr = w + (int64_t)e * W;
+__device__ __forceinline__ float router_dot(const E *__restrict__ hr, const float *__restrict__ wr, int64_t W, int lane) {
     float s = 0.f;
     if (W % 4 == 0) {
 #pragma unroll 4
@@ -34,7 +28,19 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const E *__restrict__ h
     } else {
         for (int64_t k = lane; k < W; k += 32) s = fmaf(wr[k], to_f32(hr[k]), s);
     }
-    s = warp_sum_f32(s);
+    return warp_sum_f32(s);
+}
+
+// router logits: a warp per (token, expert), z[t][e] = w[e] . h[t] + b[e] in fp32
+template <typename E>
+__global__ void __launch_bounds__(256) moe_logits_kernel(const E *__restrict__ h, int64_t W, int64_t T, const float *__restrict__ w,
+                                                         const float *__restrict__ b, int n_exp, float *__restrict__ z) {
+    const int lane = threadIdx.x & 31;
+    const int64_t i = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= T * n_exp) return;
+    const int64_t t = i / n_exp;
+    const int e = (int)(i - t * n_exp);
+    const float s = router_dot(h + t * W, w + (int64_t)e * W, W, lane);
     if (lane == 0) z[i] = s + (b ? b[e] : 0.f);
 }
 
@@ -81,14 +87,12 @@ __global__ void __launch_bounds__(32) moe_select_kernel(const float *__restrict_
 // s_e + corr_e; the experts form n_groups equal groups of neighbours, a group's score is the sum of its two largest
 // choice scores, and only experts of the `keep` best groups (ties: the lower group) can be chosen; among them the `top`
 // largest choice scores win (ties: the lower index).  The weight of a chosen expert is its plain s, not renormalised.
-__global__ void __launch_bounds__(32) moe_select_sigmoid_kernel(const float *__restrict__ zg, const float *__restrict__ corr, int n_exp, int top,
-                                                                int n_groups, int keep, int32_t *__restrict__ idx, float *__restrict__ wt) {
-    extern __shared__ float sm[]; // [n_exp] scores, [n_exp] choice scores, [n_groups] group scores
-    float *sc = sm, *ch = sm + n_exp, *gsc = ch + n_exp;
-    const int64_t t = blockIdx.x;
-    const int lane = threadIdx.x, gs = n_exp / n_groups;
+// one warp; sc holds the logits on entry (the scores afterwards), ch and gsc are scratch
+__device__ __forceinline__ void select_sigmoid_warp(float *sc, float *ch, float *gsc, const float *__restrict__ corr, int n_exp, int top, int n_groups,
+                                                    int keep, int64_t t, int lane, int32_t *__restrict__ idx, float *__restrict__ wt) {
+    const int gs = n_exp / n_groups;
     for (int e = lane; e < n_exp; e += 32) {
-        const float s = 1.0f / (1.0f + expf(-zg[t * n_exp + e]));
+        const float s = 1.0f / (1.0f + expf(-sc[e]));
         sc[e] = s;
         ch[e] = s + (corr ? corr[e] : 0.f);
     }
@@ -135,6 +139,45 @@ __global__ void __launch_bounds__(32) moe_select_sigmoid_kernel(const float *__r
     }
 }
 
+__global__ void __launch_bounds__(32) moe_select_sigmoid_kernel(const float *__restrict__ zg, const float *__restrict__ corr, int n_exp, int top,
+                                                                int n_groups, int keep, int32_t *__restrict__ idx, float *__restrict__ wt) {
+    extern __shared__ float sm[]; // [n_exp] scores, [n_exp] choice scores, [n_groups] group scores
+    for (int e = threadIdx.x; e < n_exp; e += 32) sm[e] = zg[(int64_t)blockIdx.x * n_exp + e];
+    __syncwarp();
+    select_sigmoid_warp(sm, sm + n_exp, sm + 2 * n_exp, corr, n_exp, top, n_groups, keep, blockIdx.x, threadIdx.x, idx, wt);
+}
+
+// few tokens (a step): logits and choice in ONE launch, a CTA per token, its warps an expert's logit each in turn.  With
+// row_src the slots are also listed as the mat-vec form of the grouped products reads them (slot s = row s: no order is
+// needed there), which stands in for moe_group_kernel.
+template <typename E>
+__global__ void __launch_bounds__(1024) moe_route_sigmoid_step_kernel(const E *__restrict__ h, int64_t W, const float *__restrict__ w,
+                                                                     const float *__restrict__ corr, int n_exp, int top, int n_groups, int keep,
+                                                                     float *__restrict__ zg, int32_t *__restrict__ idx, float *__restrict__ wt,
+                                                                     int32_t *__restrict__ row_src, int32_t *__restrict__ inv,
+                                                                     int32_t *__restrict__ row_expert) {
+    extern __shared__ float sm[];
+    const int64_t t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int e = warp; e < n_exp; e += (int)(blockDim.x >> 5)) {
+        const float s = router_dot(h + t * W, w + (int64_t)e * W, W, lane);
+        if (lane == 0) {
+            sm[e] = s;
+            zg[t * n_exp + e] = s;
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    select_sigmoid_warp(sm, sm + n_exp, sm + 2 * n_exp, corr, n_exp, top, n_groups, keep, t, lane, idx, wt);
+    if (row_src)
+        for (int k = lane; k < top; k += 32) {
+            const int64_t s = t * top + k;
+            row_src[s] = (int32_t)t;
+            inv[s] = (int32_t)s;
+            row_expert[s] = idx[s];
+        }
+}
+
 // one CTA: counts per expert, offsets, the list of 64-row tiles, and the sorted order of the n = T * top slots
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int32_t *__restrict__ idx, int n, int top, int n_exp, int32_t *offsets,
                                                          int32_t *row_src, int32_t *inv, int32_t *tile_expert, int32_t *tile_row0,
@@ -179,9 +222,11 @@ __global__ void __launch_bounds__(256) moe_vec_kernel(const E *__restrict__ w, i
     const int64_t n = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int row = blockIdx.y;
     if (n >= N) return;
-    const E *wr = w + ((int64_t)row_expert[row] * N + n) * K;
+    // ACT 2: an expert's matrix holds N gate rows, then N up rows; output n is silu(gate_n) * up_n
+    const E *wr = w + ((int64_t)row_expert[row] * (ACT == 2 ? 2 * N : N) + n) * K;
+    const E *wu = wr + N * K;
     const E *ar = a + (int64_t)(row_src ? row_src[row] : row) * lda;
-    float acc = 0.f;
+    float acc = 0.f, up = 0.f;
     if (vec) {
 #pragma unroll 4
         for (int64_t k = (int64_t)lane * VE; k < K; k += 32 * VE) {
@@ -189,13 +234,24 @@ __global__ void __launch_bounds__(256) moe_vec_kernel(const E *__restrict__ w, i
             const E *we = reinterpret_cast<const E *>(&wv), *ae = reinterpret_cast<const E *>(&av);
 #pragma unroll
             for (int u = 0; u < VE; u++) acc = fmaf(to_f32(we[u]), to_f32(ae[u]), acc);
+            if (ACT == 2) {
+                const uint4 uv = ldg_stream_u4(wu + k);
+                const E *ue = reinterpret_cast<const E *>(&uv);
+#pragma unroll
+                for (int u = 0; u < VE; u++) up = fmaf(to_f32(ue[u]), to_f32(ae[u]), up);
+            }
         }
     } else {
-        for (int64_t k = lane; k < K; k += 32) acc = fmaf(to_f32(wr[k]), to_f32(ar[k]), acc);
+        for (int64_t k = lane; k < K; k += 32) {
+            acc = fmaf(to_f32(wr[k]), to_f32(ar[k]), acc);
+            if (ACT == 2) up = fmaf(to_f32(wu[k]), to_f32(ar[k]), up);
+        }
     }
     acc = warp_sum_f32(acc);
+    if (ACT == 2) up = warp_sum_f32(up);
     if (lane == 0) {
         if (ACT == 1) c_act[(int64_t)row * ldc + n] = from_f32<E>(acc > 0.f ? acc * acc : 0.f);
+        else if (ACT == 2) c_act[(int64_t)row * ldc + n] = from_f32<E>(acc / (1.0f + expf(-acc)) * up);
         else c[(int64_t)row * ldc + n] = acc;
     }
 }
@@ -241,20 +297,38 @@ int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w
     return GGB_OK;
 }
 
+int ggb_moe_step_form(int64_t n_slots) { return n_slots <= 16; }
+
 int ggb_op_moe_route_sigmoid(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *correction, int n_exp, int top,
-                             int n_groups, int keep, float *logits, int32_t *idx, float *wt) {
+                             int n_groups, int keep, float *logits, int32_t *idx, float *wt, int32_t *ws) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(h && w_router && idx && wt && logits && W > 0 && T > 0 && n_exp > 0 && top > 0 && n_exp <= 4096, "moe_route_sigmoid: bad arguments");
     GGB_CHECK_ARG(n_groups > 0 && n_exp % n_groups == 0 && keep > 0 && keep <= n_groups && top <= keep * (n_exp / n_groups),
                   "moe_route_sigmoid: %d experts in %d groups of which %d stay cannot give %d experts", n_exp, n_groups, keep, top);
+    const size_t smem = (size_t)(2 * n_exp + n_groups) * 4;
+    if (T <= 32) { // a step: one launch, and the slot lists of the mat-vec form with it
+        const int64_t n = T * top;
+        const int mt = ggb_moe_max_tiles(n, n_exp);
+        const bool lists = ws && ggb_moe_step_form(n);
+        const unsigned step_threads = 32u * (unsigned)std::min(32, std::max(n_exp, 1)); // a warp per expert, up to 32 at a time
+        int32_t *row_src = lists ? ws + n_exp + 1 : nullptr, *inv = lists ? row_src + n : nullptr, *row_expert = lists ? inv + n + 2 * mt + 1 : nullptr;
+        if (dt == GGB_TYPE_BF16)
+            moe_route_sigmoid_step_kernel<<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, w_router, correction, n_exp, top, n_groups,
+                                                                                         keep, logits, idx, wt, row_src, inv, row_expert);
+        else
+            moe_route_sigmoid_step_kernel<<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>((const float *)h, W, w_router, correction, n_exp, top, n_groups, keep,
+                                                                                         logits, idx, wt, row_src, inv, row_expert);
+        GGB_LAUNCH_CHECK();
+        return GGB_OK;
+    }
     const unsigned blocks = (unsigned)((T * n_exp + 7) / 8);
     if (dt == GGB_TYPE_BF16)
         moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, T, w_router, nullptr, n_exp, logits);
     else
         moe_logits_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((const float *)h, W, T, w_router, nullptr, n_exp, logits);
     GGB_LAUNCH_CHECK();
-    moe_select_sigmoid_kernel<<<(unsigned)T, 32, (size_t)(2 * n_exp + n_groups) * 4, ggb_cuda_stream()>>>(logits, correction, n_exp, top, n_groups,
+    moe_select_sigmoid_kernel<<<(unsigned)T, 32, smem, ggb_cuda_stream()>>>(logits, correction, n_exp, top, n_groups,
                                                                                                          keep, idx, wt);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
@@ -291,15 +365,17 @@ int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a
                       const int32_t *ws, int act, void *c, int64_t ldc) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
-    GGB_CHECK_ARG(w && a && ws && c && N > 0 && K > 0 && T > 0 && lda >= K && ldc >= N, "moe_linear: bad arguments");
+    GGB_CHECK_ARG(w && a && ws && c && N > 0 && K > 0 && T > 0 && lda >= K && ldc >= N && act >= 0 && act <= 2, "moe_linear: bad arguments");
+    GGB_CHECK_ARG(act != 2 || ggb_moe_step_form(T * top), "moe_linear: the gated form is built for steps of at most 16 slots");
     const ggb_moe_groups g = groups_of(const_cast<int32_t *>(ws), T * top, n_exp, gather != 0);
-    if (T * top <= 16) { // decode: every slot is a mat-vec on its expert's matrix
+    if (ggb_moe_step_form(T * top)) { // decode: every slot is a mat-vec on its expert's matrix
         const int es = dt == GGB_TYPE_BF16 ? 2 : 4;
         const int vec = K % (16 / es) == 0 && lda % (16 / es) == 0 && ((uintptr_t)w | (uintptr_t)a) % 16 == 0;
         const int32_t *row_expert = g.n_tiles + 1;
         const dim3 grid((unsigned)((N + 7) / 8), (unsigned)(T * top));
 #define MV(E)                                                                                                                         \
-    if (act) moe_vec_kernel<E, 1><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, nullptr, (E *)c, ldc, vec); \
+    if (act == 2) moe_vec_kernel<E, 2><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, nullptr, (E *)c, ldc, vec); \
+    else if (act) moe_vec_kernel<E, 1><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, nullptr, (E *)c, ldc, vec); \
     else moe_vec_kernel<E, 0><<<grid, 256, 0, ggb_cuda_stream()>>>((const E *)w, N, K, (const E *)a, lda, g.row_src, row_expert, (float *)c, nullptr, ldc, vec);
         if (dt == GGB_TYPE_BF16) { MV(__nv_bfloat16) } else { MV(float) }
 #undef MV
@@ -328,6 +404,12 @@ int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a
     }
     return ggb_linear_grouped_launch(dt, w, N, K, a, lda, ggb_moe_max_tiles(T * top, n_exp), act ? nullptr : (float *)c, act ? c : nullptr,
                                      ldc, act, g);
+}
+
+int ggb_op_moe_combine_norm(int dt, const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, const float *wa,
+                            float eps, float *x, const float *wy, void *out) {
+    GGB_CHECK_ARG(y && ws && wt && top > 0 && n_exp > 0, "moe_combine_norm: bad arguments");
+    return ggb_norm_add_norm_launch(dt, y, nullptr, ws + n_exp + 1 + T * top, wt, top, wa, eps, W, T, x, wy, out);
 }
 
 int ggb_op_moe_combine(const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, float *out) {

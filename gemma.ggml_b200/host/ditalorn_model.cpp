@@ -401,8 +401,8 @@ int ditalorn_model::emit(int T, int ns, const int32_t *table, float *state, int 
     const dl_config &c = cfg_;
     const int64_t W = c.width, t = T;
     const int B = cache_->page_size();
-    DL_OP("op_rows", ggb_op_embed_pos(dt_, embed_, pos_, ids_, pos0_, t, W, c.embed_scale, x_));
-    DL_OP("op_norm", ggb_op_rms_norm2(dt_, x_, W, lw_[0].norm1, 1, nullptr, 0, c.eps, W, t, h_, nullptr));
+    // the embedding and the first layer's norm in one pass
+    DL_OP("op_rows", ggb_op_embed_pos(dt_, embed_, pos_, ids_, pos0_, t, W, c.embed_scale, x_, lw_[0].norm1, c.eps, h_));
     for (size_t li = 0; li < c.layers.size(); li++) {
         const dl_layer_cfg &l = c.layers[li];
         const dl_layer_w &w = lw_[li];
@@ -439,13 +439,25 @@ int ditalorn_model::emit(int T, int ns, const int32_t *table, float *state, int 
         DL_OP("op_residual", ggb_op_norm_add_norm(dt_, ya_, mixer_bias, w.norm1b, c.eps, W, t, x_, after, after ? h_ : nullptr));
         if (ff) {
             const dl_moe_cfg &E = l.moe;
-            DL_OP("op_moe", ggb_op_moe_route_sigmoid(dt_, h_, W, t, w.router, w.correction, E.experts, E.top, E.groups, E.keep, route_z_, route_i_, route_w_));
-            DL_OP("op_moe", ggb_op_moe_group(route_i_, t, E.top, E.experts, group_ws_));
-            DL_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_gate_up, 2 * (int64_t)E.ff, W, h_, W, 1, t, E.top, E.experts, group_ws_, 0, gu_, 2 * (int64_t)E.ff));
-            DL_OP("op_act", ggb_op_glu_bias(dt_, gu_, E.ff, t * E.top, nullptr, nullptr, 1, act_));
+            // a step of few slots: the router lists the slots itself and every slot is a mat-vec with the gate folded in
+            const bool step = ggb_moe_step_form(t * E.top) != 0;
+            DL_OP("op_moe", ggb_op_moe_route_sigmoid(dt_, h_, W, t, w.router, w.correction, E.experts, E.top, E.groups, E.keep, route_z_, route_i_, route_w_,
+                                                     group_ws_));
+            if (step) {
+                DL_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_gate_up, E.ff, W, h_, W, 1, t, E.top, E.experts, group_ws_, 2, act_, E.ff));
+            } else {
+                DL_OP("op_moe", ggb_op_moe_group(route_i_, t, E.top, E.experts, group_ws_));
+                DL_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_gate_up, 2 * (int64_t)E.ff, W, h_, W, 1, t, E.top, E.experts, group_ws_, 0, gu_, 2 * (int64_t)E.ff));
+                DL_OP("op_act", ggb_op_glu_bias(dt_, gu_, E.ff, t * E.top, nullptr, nullptr, 1, act_));
+            }
             DL_OP("op_moe_linear", ggb_op_moe_linear(dt_, w.e_down, W, E.ff, act_, E.ff, 0, t, E.top, E.experts, group_ws_, 0, y2_, W));
-            DL_OP("op_moe", ggb_op_moe_combine(y2_, group_ws_, route_w_, t, E.top, E.experts, W, ya_));
-            DL_OP("op_residual", ggb_op_norm_add_norm(dt_, ya_, nullptr, w.norm2b, c.eps, W, t, x_, next_norm, next_norm ? h_ : nullptr));
+            // the weighted sum of the slots, x += norm2b(.), and the norm in front of the next layer, in one pass
+            if (E.top <= GGB_MOE_COMBINE_NORM_MAX_TOP) {
+                DL_OP("op_residual", ggb_op_moe_combine_norm(dt_, y2_, group_ws_, route_w_, t, E.top, E.experts, W, w.norm2b, c.eps, x_, next_norm, next_norm ? h_ : nullptr));
+            } else {
+                DL_OP("op_moe", ggb_op_moe_combine(y2_, group_ws_, route_w_, t, E.top, E.experts, W, ya_));
+                DL_OP("op_residual", ggb_op_norm_add_norm(dt_, ya_, nullptr, w.norm2b, c.eps, W, t, x_, next_norm, next_norm ? h_ : nullptr));
+            }
         }
         if (capture_ && cap_) DL_OP("op_rows", ggb_op_gather_rows_f32(x_, iota_, t, W, cap_ + li * (size_t)max_T_ * (size_t)W));
     }

@@ -289,9 +289,10 @@ int ggb_op_softcap(float *x, int64_t n, float cap);
  * act(gate) with gate fp32 rows of stride ldg; act 0: sigmoid, 1: silu; y in dt, dense [T][n_groups * gs] */
 int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int64_t ldg, int64_t T, int n_groups, int gs, const float *w,
                      int w_period, float eps, int act, void *y);
-/* token embedding with learned positions: y[t] = table[ids[t]] * scale + pos_table[*pos0 + t] (pos_table may be NULL) */
+/* token embedding with learned positions: y[t] = table[ids[t]] * scale + pos_table[*pos0 + t] (pos_table may be NULL);
+ * with yn also the first layer's norm in the same pass: yn (dt) = y / sqrt(mean(y^2) + eps) * wn */
 int ggb_op_embed_pos(int dt, const void *table, const void *pos_table, const int32_t *ids, const int32_t *pos0, int64_t T, int64_t E,
-                     float scale, float *y);
+                     float scale, float *y, const float *wn, float eps, void *yn);
 /* norms on both sides of a sublayer in one pass over the row: v = a (+ bias); x += v / sqrt(mean(v^2) + eps) * wa; then,
  * with y, y (dt) = x / sqrt(mean(x^2) + eps) * wy: the input of the next sublayer.  Weights as they multiply (a weight
  * stored around zero is handed in as 1 + w). */
@@ -404,13 +405,22 @@ int ggb_op_moe_route(int dt, const void *h, int64_t W, int64_t T, const float *w
  * scores, and only the `keep` best groups can be chosen from (ties: the lower index, for groups and experts); the `top`
  * largest choice scores win and the weights are their s, not renormalised */
 int ggb_op_moe_route_sigmoid(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *correction, int n_exp, int top,
-                             int n_groups, int keep, float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt);
+                             int n_groups, int keep, float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt, int32_t *ws);
+/* 1 when a step of n_slots = T * top slots takes the mat-vec form of the grouped products.  Then route_sigmoid, given ws
+ * (ggb_moe_group_ints), also lists the slots there in the same launch and ggb_op_moe_group may be left out, and
+ * moe_linear takes act 2: w = [n_exp][2 N][K] (N gate rows, then N up rows), c (dt) = silu(gate) * up. */
+int ggb_moe_step_form(int64_t n_slots);
 int ggb_moe_max_tiles(int64_t n_slots, int n_exp);
 size_t ggb_moe_group_ints(int64_t n_slots, int n_exp);
 int ggb_op_moe_group(const int32_t *idx, int64_t T, int top, int n_exp, int32_t *ws);
 int ggb_op_moe_linear(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int gather, int64_t T, int top, int n_exp,
                       const int32_t *ws, int act, void *c, int64_t ldc);
 int ggb_op_moe_combine(const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, float *out);
+/* combine and the norms on both sides of the sublayer (ggb_op_norm_add_norm) in one pass: v = sum_s wt[t][s] y[slot s];
+ * x += v / rms(v) * wa; out (dt, may be NULL) = x / rms(x) * wy */
+#define GGB_MOE_COMBINE_NORM_MAX_TOP 64 /* more slots per token: ggb_op_moe_combine, then ggb_op_norm_add_norm */
+int ggb_op_moe_combine_norm(int dt, const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, const float *wa,
+                            float eps, float *x, const float *wy, void *out);
 
 /* ------------------------------------------------------------------ fused decode step
  * The whole per-token node list (ref: src/gemma_model.cpp:665-747) as ONE persistent cooperative

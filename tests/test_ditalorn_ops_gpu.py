@@ -62,10 +62,15 @@ def test_embedding_with_learned_positions(gpu, dt):
     tv, tu = as_dt(dt, r.standard_normal((V, E)))
     pv, pu = as_dt(dt, r.standard_normal((n_pos, E)))
     ids = r.integers(0, V, T).astype(np.int32)
-    y = zeros(gpu, T * E * 4)
+    wn = f32(0.3 * r.standard_normal(E))
+    y, yn = zeros(gpu, T * E * 4), zeros(gpu, T * E * 4)
     gpu.check(gpu.cuda_lib().ggb_op_embed_pos(dt, dev(gpu, tu).ptr, dev(gpu, pu).ptr, dev(gpu, ids).ptr, dev(gpu, np.array([p0], dtype=np.int32)).ptr,
-                                              T, E, 2.5, y.ptr), "embed_pos")
-    assert F.rel_err(y.download(np.float32, T * E).reshape(T, E), P.embed(ids, tv, pv, 2.5, p0)) < 1e-6
+                                              T, E, 2.5, y.ptr, dev(gpu, f32(1 + wn)).ptr, 1e-3, yn.ptr), "embed_pos")
+    want = P.embed(ids, tv, pv, 2.5, p0)
+    assert F.rel_err(y.download(np.float32, T * E).reshape(T, E), want) < 1e-6
+    assert F.rel_err(from_dt(dt, yn, (T, E)), P.norm_centered(want, wn.astype(np.float64), 1e-3)) < (5e-3 if dt == BF16 else 1e-6)
+    gpu.check(gpu.cuda_lib().ggb_op_embed_pos(dt, dev(gpu, tu).ptr, None, dev(gpu, ids).ptr, None, T, E, 1.0, y.ptr, None, 0.0, None), "embed_pos")
+    assert F.rel_err(y.download(np.float32, T * E).reshape(T, E), tv[ids]) < 1e-6
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
@@ -113,7 +118,7 @@ def run_route(gpu, dt, h, router, corr, top, n_groups, keep):
     _, hu = as_dt(dt, h)
     z, idx, wt = zeros(gpu, T * E * 4), zeros(gpu, T * top * 4), zeros(gpu, T * top * 4)
     gpu.check(gpu.cuda_lib().ggb_op_moe_route_sigmoid(dt, dev(gpu, hu).ptr, W, T, dev(gpu, f32(router)).ptr, ptr(dev(gpu, f32(corr))) if corr is not None else None,
-                                                      E, top, n_groups, keep, z.ptr, idx.ptr, wt.ptr), "route")
+                                                      E, top, n_groups, keep, z.ptr, idx.ptr, wt.ptr, None), "route")
     return idx.download(np.int32, T * top).reshape(T, top), wt.download(np.float32, T * top).reshape(T, top)
 
 
@@ -131,6 +136,8 @@ def test_router_sigmoid_groups_and_correction(gpu, dt, E, top, n_groups, keep):
     assert np.abs(wt - want_w).max() < 1e-6
     plain_i, _ = P.route(hv, router, np.zeros(E), top, n_groups, keep)
     assert (plain_i != want_i).any()  # the correction did matter, and the weights above are the uncorrected scores
+    idx, wt = run_route(gpu, dt, hv[:5], router, corr, top, n_groups, keep)  # few tokens: logits and choice in one launch
+    assert (idx == want_i[:5]).all() and np.abs(wt - want_w[:5]).max() < 1e-6
 
 
 def test_router_group_of_negative_scores_beats_an_excluded_one(gpu):
@@ -317,3 +324,45 @@ def test_latent_window_edge_with_one_key_standing_out(gpu, dt, steps):
         got = run_latent(gpu, dt, d, q, wuk, wuv, None, nw, H, D, Dv, window, 1.0, cuts, page, 2 if steps == "portion" else 4, seed=i)
         assert np.abs(got[i] - want[i]).max() < (5e-2 if dt == BF16 else 2e-5), (window, i, j)
         assert F.rel_err(got, want) < (2e-2 if dt == BF16 else 5e-6), (window, i, j)
+
+
+# ------------------------------------------------------------------------------------------------ experts end to end
+@pytest.mark.parametrize("dt", [F32, BF16])
+@pytest.mark.parametrize("T", [1, 3, 8, 40])
+def test_experts_in_step_form_and_in_portion_form(gpu, dt, T):
+    """router -> slots -> gated experts -> weighted sum -> norms on both sides, as the model chains them: a step of few
+    slots (the router lists the slots, gate and up in one mat-vec) and a portion (sorted slots, tiles) give the oracle's sum"""
+    lib = gpu.cuda_lib()
+    r = np.random.default_rng(T)
+    W, E, ff, top, n_groups, keep, eps = 24, 6, 10, 2, 3, 2, 1e-5
+    f = {"router": {"experts": E, "top": top, "groups": {"count": n_groups, "keep": keep}}}
+    w = {"router": f32(r.standard_normal((E, W)) / 4).astype(np.float64), "correction": f32(0.3 * r.standard_normal(E)).astype(np.float64)}
+    gu, dn = [], []
+    for e in range(E):
+        for n, shape in (("gate", (ff, W)), ("up", (ff, W)), ("down", (W, ff))):
+            w["e%d.%s" % (e, n)], _ = as_dt(dt, r.standard_normal(shape) / np.sqrt(shape[1]))
+        gu += [w["e%d.gate" % e], w["e%d.up" % e]]
+        dn.append(w["e%d.down" % e])
+    hv, hu = as_dt(dt, r.standard_normal((T, W)))
+    x0, wa, wy = f32(r.standard_normal((T, W))), f32(0.2 * r.standard_normal(W)), f32(0.2 * r.standard_normal(W))
+    n, es = T * top, 2 if dt == BF16 else 4
+    z, idx, wt = zeros(gpu, T * E * 4), zeros(gpu, n * 4), zeros(gpu, n * 4)
+    ws = zeros(gpu, lib.ggb_moe_group_ints(n, E) * 4)
+    guw, dnw, hd = dev(gpu, as_dt(dt, np.concatenate(gu))[1]), dev(gpu, as_dt(dt, np.concatenate(dn))[1]), dev(gpu, hu)
+    act, y2, x, out = zeros(gpu, n * ff * es), zeros(gpu, n * W * 4), dev(gpu, x0), zeros(gpu, T * W * es)
+    gpu.check(lib.ggb_op_moe_route_sigmoid(dt, hd.ptr, W, T, dev(gpu, f32(w["router"])).ptr, dev(gpu, f32(w["correction"])).ptr, E, top, n_groups, keep, z.ptr,
+                                           idx.ptr, wt.ptr, ws.ptr), "route")
+    if lib.ggb_moe_step_form(n):
+        assert n <= 16
+        gpu.check(lib.ggb_op_moe_linear(dt, guw.ptr, ff, W, hd.ptr, W, 1, T, top, E, ws.ptr, 2, act.ptr, ff), "gate_up")
+    else:
+        gbuf = zeros(gpu, n * 2 * ff * 4)
+        gpu.check(lib.ggb_op_moe_group(idx.ptr, T, top, E, ws.ptr), "group")
+        gpu.check(lib.ggb_op_moe_linear(dt, guw.ptr, 2 * ff, W, hd.ptr, W, 1, T, top, E, ws.ptr, 0, gbuf.ptr, 2 * ff), "gate_up")
+        gpu.check(lib.ggb_op_glu_bias(dt, gbuf.ptr, ff, n, None, None, 1, act.ptr), "glu")
+    gpu.check(lib.ggb_op_moe_linear(dt, dnw.ptr, W, ff, act.ptr, ff, 0, T, top, E, ws.ptr, 0, y2.ptr, W), "down")
+    gpu.check(lib.ggb_op_moe_combine_norm(dt, y2.ptr, ws.ptr, wt.ptr, T, top, E, W, dev(gpu, f32(1 + wa)).ptr, eps, x.ptr, dev(gpu, f32(1 + wy)).ptr, out.ptr), "combine_norm")
+    x2 = x0 + P.norm_centered(P.moe(hv, w, f), wa.astype(np.float64), eps)
+    tol = 2e-2 if dt == BF16 else 5e-6
+    assert F.rel_err(x.download(np.float32, T * W).reshape(T, W), x2) < tol
+    assert F.rel_err(from_dt(dt, out, (T, W)), P.norm_centered(x2, wy.astype(np.float64), eps)) < tol
