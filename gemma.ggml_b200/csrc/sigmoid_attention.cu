@@ -171,18 +171,21 @@ __global__ void __launch_bounds__(32) sigmoid_merge_kernel(const float *__restri
     }
 }
 
-// ---- portions: 32 tokens of one head per CTA, tiles of 32 cache rows staged in shared memory
-template <typename E>
+// ---- portions: 32 tokens of one head per CTA, tiles of 32 cache rows staged in shared memory.
+// NR: groups of 32 value coordinates a lane accumulates (Dv <= 32 NR).  VEC: rows are staged and K rows read in 16-byte
+// pieces; the K pitch kp is then a multiple of 4 words with kp / 4 odd, so that the eight lanes of a quarter warp, a row
+// each, cover all 32 banks.
+template <typename E, int NR, bool VEC>
 __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                         const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
-                                                                        int64_t T, int H, int G, int D, int Dv, int64_t window,
+                                                                        int64_t T, int H, int G, int D, int Dv, int kp, int vp, int64_t window,
                                                                         const float *__restrict__ r1, const float *__restrict__ r2,
-                                                                        const float *__restrict__ pb, E *__restrict__ out, int vec) {
+                                                                        const float *__restrict__ pb, E *__restrict__ out) {
     extern __shared__ __align__(16) float sa_smem[];
     __shared__ float pen[64]; // pen[31 + qi - lane]: the penalty of distance (i0 - j0) + qi - lane
-    const int Dp = (D + 3) & ~3, kp = D | 1, vp = Dv;
+    const int Dp = (D + 3) & ~3;
     float *sq = sa_smem;       // [kQT][Dp]
-    float *sk = sq + kQT * Dp; // [32][kp]: odd pitch, lane = row reads are conflict-free
+    float *sk = sq + kQT * Dp; // [32][kp]: lane = row reads are conflict-free
     float *sv = sk + 32 * kp;  // [32][vp]: lane = column reads
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int h = blockIdx.y, g = h / (H / G);
@@ -195,11 +198,11 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
     }
     const float hr1 = r1 ? r1[h] : 0.f, hr2 = r2 ? r2[h] : 0.f, hpb = pb ? pb[h] : 0.f;
     const int64_t jlo = window > 0 ? max((int64_t)0, i0 - window + 1) : 0;
-    float acc[kQPW][kMaxDvRegs];
+    float acc[kQPW][NR];
 #pragma unroll
     for (int a = 0; a < kQPW; a++)
 #pragma unroll
-        for (int r = 0; r < kMaxDvRegs; r++) acc[a][r] = 0.f;
+        for (int r = 0; r < NR; r++) acc[a][r] = 0.f;
     const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
     for (int64_t j0 = jlo; j0 <= i_last; j0 += 32) {
         __syncthreads(); // the previous tile has been consumed (and sq is written, the first time)
@@ -208,7 +211,7 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
         for (int rr = warp; rr < 32; rr += kWarps) {
             const int64_t j = j0 + min(rr, n_rows - 1); // a row past the last one repeats it (weight 0 below)
             const E *row = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld;
-            if (vec) {
+            if (VEC) {
                 constexpr int VN = RowVec<E>::n;
                 const int nk = D / VN, nv = Dv / VN;
                 for (int vi = lane; vi < nk + nv; vi += 32) {
@@ -216,9 +219,9 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
                     const int c = (is_k ? vi : vi - nk) * VN;
                     RowVec<E> x;
                     x.raw = *reinterpret_cast<const uint4 *>(row + (is_k ? koff : voff) + c);
-                    float *dst = is_k ? sk + rr * kp + c : sv + rr * vp + c;
+                    float4 *dst = reinterpret_cast<float4 *>(is_k ? sk + rr * kp + c : sv + rr * vp + c);
 #pragma unroll
-                    for (int u = 0; u < VN; u++) dst[u] = x.at(u);
+                    for (int u = 0; u < VN; u += 4) dst[u / 4] = make_float4(x.at(u), x.at(u + 1), x.at(u + 2), x.at(u + 3));
                 }
             } else {
                 for (int c = lane; c < D + Dv; c += 32) {
@@ -235,7 +238,13 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
         const int D4 = D & ~3;
 #pragma unroll 2
         for (int d = 0; d < D4; d += 4) {
-            const float k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
+            float k0, k1, k2, k3;
+            if (VEC) {
+                const float4 kv = *reinterpret_cast<const float4 *>(kr + d);
+                k0 = kv.x, k1 = kv.y, k2 = kv.z, k3 = kv.w;
+            } else {
+                k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
+            }
 #pragma unroll
             for (int a = 0; a < kQPW; a++) {
                 const float4 qv = *reinterpret_cast<const float4 *>(sq + (warp * kQPW + a) * Dp + d);
@@ -257,12 +266,13 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
             const bool vis = qi < nq && j <= i && (window <= 0 || i - j < window);
             p[a] = vis ? sigmoid_f32(s[a] - pen[31 + qi - lane] + hpb) : 0.f;
         }
+#pragma unroll 2
         for (int jj = 0; jj < n_rows; jj++) {
             float pj[kQPW];
 #pragma unroll
             for (int a = 0; a < kQPW; a++) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
 #pragma unroll
-            for (int r = 0; r < kMaxDvRegs; r++) {
+            for (int r = 0; r < NR; r++) {
                 const int c = lane + 32 * r;
                 if (c < Dv) {
                     const float vv = sv[jj * vp + c];
@@ -277,7 +287,7 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_tile_kernel(const fl
         const int qi = warp * kQPW + a;
         if (qi >= nq) continue;
 #pragma unroll
-        for (int r = 0; r < kMaxDvRegs; r++) {
+        for (int r = 0; r < NR; r++) {
             const int c = lane + 32 * r;
             if (c < Dv) out[((t0 + qi) * H + h) * Dv + c] = from_f32<E>(acc[a][r]);
         }
@@ -324,17 +334,35 @@ int ggb_op_sigmoid_attn(int dt, const float *q, const void *cache, const int32_t
     const int vec = D % vn == 0 && ((int64_t)G * D) % vn == 0 && ((uintptr_t)cache % 16 == 0);
     cudaStream_t st = ggb_cuda_stream();
     if (T >= kQT) {
-        const size_t smem = ((size_t)kQT * Dp + 32 * (size_t)(D | 1) + 32 * (size_t)Dv) * 4;
+        const bool tv = vec && Dv % vn == 0;
+        int kp = D | 1, vp = Dv;
+        if (tv) { // 16-byte pieces: K rows a multiple of 4 words apart with an odd number of pieces, V rows whole pieces
+            kp = (D + 3) & ~3;
+            if ((kp / 4) % 2 == 0) kp += 4;
+            vp = (Dv + 3) & ~3;
+        }
+        const size_t smem = ((size_t)kQT * Dp + 32 * (size_t)kp + 32 * (size_t)vp) * 4;
         GGB_CHECK_ARG(smem <= 200 * 1024, "sigmoid_attn: head sizes %d / %d do not fit shared memory", D, Dv);
         const dim3 grid((unsigned)((T + kQT - 1) / kQT), (unsigned)H);
-#define ST_LAUNCH(ET)                                                                                                          \
+#define ST_LAUNCH(ET, NR, VEC)                                                                                                 \
     {                                                                                                                          \
-        auto kfn = sigmoid_attn_tile_kernel<ET>;                                                                               \
+        auto kfn = sigmoid_attn_tile_kernel<ET, NR, VEC>;                                                                      \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));      \
-        kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, \
-                                             r1, r2, pb, (ET *)out, vec && Dv % vn == 0);                                      \
+        kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, kp, vp, \
+                                             window, r1, r2, pb, (ET *)out);                                                   \
     }
-        if (dt == GGB_TYPE_BF16) ST_LAUNCH(__nv_bfloat16) else ST_LAUNCH(float)
+#define ST_NR(ET, VEC)                         \
+    {                                          \
+        if (Dv <= 64) ST_LAUNCH(ET, 2, VEC)    \
+        else if (Dv <= 128) ST_LAUNCH(ET, 4, VEC) \
+        else ST_LAUNCH(ET, 8, VEC)             \
+    }
+        if (dt == GGB_TYPE_BF16) {
+            if (tv) ST_NR(__nv_bfloat16, true) else ST_NR(__nv_bfloat16, false)
+        } else {
+            if (tv) ST_NR(float, true) else ST_NR(float, false)
+        }
+#undef ST_NR
 #undef ST_LAUNCH
     } else {
         const size_t smem = (size_t)kWarps * Dp * 4 + (size_t)kWarps * kMaxDvRegs * 32 * 4;
