@@ -164,6 +164,8 @@ _CUDA_SIG = {
     "ggb_op_norm_add_norm": (i32, [i32, vp, vp, vp, f32, i64, i64, vp, vp, vp]),
     "ggb_op_causal_conv_bias": (i32, [i32, vp, i64, i64, i64, vp, vp, i32, i32, i32, vp, vp, i64, vp]),
     "ggb_op_latent_attn_window": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i64, i32, vp]),
+    "ggb_op_latent_expand": (i32, [i32, vp, vp, i32, i64, i64, i32, i32, vp, i64, vp, vp, vp, i64]),
+    "ggb_op_head_gate": (i32, [i32, vp, i64, i32, i32, vp, i64]),
     "ggb_op_latent_attn_out_gated": (i32, [i32, vp, i32, vp, vp, i64, i32, i32, i32, vp, i64, vp]),
     "ggb_op_sigmoid_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, i32, f32, f32, vp, vp, i32, vp, vp]),
     "ggb_sigmoid_attn_scratch_bytes": (sz, [i32]),

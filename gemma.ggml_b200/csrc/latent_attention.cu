@@ -410,6 +410,29 @@ __global__ void __launch_bounds__(256) latent_attn_out_kernel(const float *__res
     }
 }
 
+// ---- the materialised form for portions: the latents of a range of positions as dense rows, and the gate on a head's output
+template <typename E>
+__global__ void latent_gather_kernel(const E *__restrict__ cache, int64_t ldk, const int32_t *__restrict__ table, int B, int64_t first, int R,
+                                     E *__restrict__ out) {
+    const E *row = cache + cache_row(table, B, first + blockIdx.x) * ldk;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) out[(int64_t)blockIdx.x * R + i] = row[i];
+}
+
+template <typename E>
+__global__ void cvt_rows_kernel(const float *__restrict__ x, int64_t n, E *__restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = from_f32<E>(x[i]);
+}
+
+template <typename E>
+__global__ void head_gate_kernel(E *__restrict__ x, int64_t T, int H, int Dv, const float *__restrict__ gate, int64_t ldg) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * H * Dv) return;
+    const int64_t t = i / ((int64_t)H * Dv);
+    const int h = (int)((i - t * H * Dv) / Dv);
+    x[i] = from_f32<E>(to_f32(x[i]) * (1.0f / (1.0f + expf(-gate[t * ldg + h]))));
+}
+
 template <typename E>
 int attn_partial_launch(const float *qa, const void *cache, int64_t ldk, const int32_t *table, int B, const int32_t *pos0, int64_t T, int H,
                         int R, int Dr, int n_split, int64_t window, float *part) {
@@ -486,6 +509,39 @@ int ggb_op_latent_q_absorb(int dt, const float *q, int64_t ldq, int64_t T, int H
     else
         latent_q_absorb_kernel<<<grid, 256, smem, ggb_cuda_stream()>>>(q, ldq, T, H, D, Dr, rot_dims, cos_sin, pos0, (const float *)w_uk, R,
                                                                        scale, qa);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_latent_expand(int dt, const void *cache, const int32_t *block_table, int block_size, int64_t first, int64_t n, int R, int Dr,
+                         const void *w_ukv, int64_t N, void *c_rows, float *kv_f32, void *kv, int64_t ld_kv) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(cache && block_table && w_ukv && c_rows && kv && block_size > 0 && first >= 0 && n > 0 && R > 0 && Dr >= 0 && N > 0 && ld_kv >= N &&
+                      (dt == GGB_TYPE_F32 || kv_f32),
+                  "latent_expand: bad arguments");
+    const int64_t ldk = ggb_latent_cache_ld(R, Dr);
+    if (dt == GGB_TYPE_BF16)
+        latent_gather_kernel<<<(unsigned)n, 128, 0, ggb_cuda_stream()>>>((const __nv_bfloat16 *)cache, ldk, block_table, block_size, first, R, (__nv_bfloat16 *)c_rows);
+    else
+        latent_gather_kernel<<<(unsigned)n, 128, 0, ggb_cuda_stream()>>>((const float *)cache, ldk, block_table, block_size, first, R, (float *)c_rows);
+    GGB_LAUNCH_CHECK();
+    // keys and values of every head in one product: rows [k (H D) | v (H Dv)], the row layout of the window attention's cache
+    if (dt == GGB_TYPE_F32) return ggb_op_linear(dt, w_ukv, N, R, c_rows, R, n, (float *)kv, ld_kv);
+    const int rc = ggb_op_linear(dt, w_ukv, N, R, c_rows, R, n, kv_f32, ld_kv);
+    if (rc) return rc;
+    cvt_rows_kernel<<<(unsigned)((n * ld_kv + 255) / 256), 256, 0, ggb_cuda_stream()>>>(kv_f32, n * ld_kv, (__nv_bfloat16 *)kv);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_head_gate(int dt, void *x, int64_t T, int H, int Dv, const float *gate, int64_t ldg) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(x && gate && T > 0 && H > 0 && Dv > 0 && ldg >= H, "head_gate: bad arguments");
+    const unsigned blocks = (unsigned)((T * H * Dv + 255) / 256);
+    if (dt == GGB_TYPE_BF16) head_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((__nv_bfloat16 *)x, T, H, Dv, gate, ldg);
+    else head_gate_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>((float *)x, T, H, Dv, gate, ldg);
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

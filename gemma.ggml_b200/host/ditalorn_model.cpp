@@ -236,8 +236,10 @@ int ditalorn_model::load(const safetensors_file *file, uint64_t seed) {
             DL_TRY(upload_matrix(a, &w.uq));
             DL_GET(m + "uk", HD, A.kv_rank, amp(A.kv_rank), 0.f, &a);
             DL_TRY(upload_matrix(a, &w.uk));
-            DL_GET(m + "uv", HV, A.kv_rank, amp(A.kv_rank), 0.f, &a);
-            DL_TRY(upload_matrix(a, &w.uv));
+            DL_GET(m + "uv", HV, A.kv_rank, amp(A.kv_rank), 0.f, &b);
+            DL_TRY(upload_matrix(b, &w.uv));
+            a.insert(a.end(), b.begin(), b.end());
+            DL_TRY(upload_matrix(a, &w.ukv));
             DL_GET(m + "o", W, HV, amp(HV), 0.f, &a);
             DL_TRY(upload_matrix(a, &w.o));
         }
@@ -349,6 +351,19 @@ int ditalorn_model::alloc_scratch() {
     }
     part_rows_ = std::max<int64_t>(T, 320);
     const size_t es = ggb_dtype_size(dt_);
+    // the materialised form of the latent attention: room for the widest visible range of a portion, if that is modest
+    int64_t ldkv = 0, rmax = 0;
+    kv_rows_ = 0;
+    for (const dl_layer_cfg &l : c.layers)
+        if (l.type == 1) {
+            const dl_latent_cfg &A = l.latent;
+            const int64_t rows = std::min<int64_t>(max_pos_, A.window > 0 ? A.window + T : max_pos_);
+            if (!materialise(A, (int)T)) continue;
+            kv_rows_ = std::max(kv_rows_, rows);
+            ldkv = std::max(ldkv, ggb_window_cache_ld(A.heads, A.dim, A.vdim));
+            rmax = std::max(rmax, (int64_t)A.kv_rank);
+        }
+    if ((size_t)kv_rows_ * (size_t)ldkv * (4 + es) > ((size_t)512 << 20)) kv_rows_ = 0; // too much: the absorbed form everywhere
     auto alloc = [&](size_t bytes, void **p) -> int {
         DL_TRY(ggb_buffer_alloc(std::max<size_t>(bytes, 16), p));
         owned_.push_back(*p);
@@ -380,6 +395,17 @@ int ditalorn_model::alloc_scratch() {
     DL_ALLOC(xw_, T * W * 4);
     DL_ALLOC(hw_, T * W * es);
     DL_ALLOC(logits_, T * (int64_t)c.vocab * 4);
+    DL_ALLOC(posrel_, c.layers.size() * 4);
+    if (kv_rows_ > 0) {
+        DL_ALLOC(crows_, kv_rows_ * rmax * es);
+        DL_ALLOC(kv_, kv_rows_ * ldkv * es);
+        if (dt_ == GGB_TYPE_BF16) DL_ALLOC(kvf_, kv_rows_ * ldkv * 4);
+        const int64_t np = kv_rows_ / cache_->page_size() + 2;
+        DL_ALLOC(page_iota_, np * 4);
+        std::vector<int32_t> pi((size_t)np);
+        for (int64_t i = 0; i < np; i++) pi[(size_t)i] = (int32_t)i;
+        DL_TRY(ggb_upload(page_iota_, pi.data(), (size_t)np * 4));
+    }
 #undef DL_ALLOC
     std::vector<int32_t> iota((size_t)T);
     for (int64_t i = 0; i < T; i++) iota[(size_t)i] = (int32_t)i;
@@ -396,8 +422,15 @@ int ditalorn_model::bind_cache(paged_cache *cache, int64_t max_positions) {
     return alloc_scratch();
 }
 
+// The absorbed form scores against the latent (2 R multiply-adds per key and head, twice); the materialised form multiplies
+// the visible latents by [W_uk; W_uv] once per portion (a tensor-core product) and then pays D + Dv per key and head in the
+// window attention kernel.  Portions take the second when heads are short beside the latent; steps always take the first.
+bool ditalorn_model::materialise(const dl_latent_cfg &a, int T) const {
+    return T >= 32 && a.vdim % 2 == 0 && a.vdim <= 256 && 4 * (int64_t)(a.dim + a.vdim) <= 5 * (int64_t)a.kv_rank && !getenv("GGB_LATENT_ABSORBED");
+}
+
 // ------------------------------------------------------------------------------------------------ one portion
-int ditalorn_model::emit(int T, int ns, const int32_t *table, float *state, int n_want) {
+int ditalorn_model::emit(int T, int64_t pos0, int ns, const int32_t *table, float *state, int n_want) {
     const dl_config &c = cfg_;
     const int64_t W = c.width, t = T;
     const int B = cache_->page_size();
@@ -429,9 +462,18 @@ int ditalorn_model::emit(int T, int ns, const int32_t *table, float *state, int 
             DL_OP("op_norm", ggb_op_rms_norm2(dt_, pr_, N, w.dq_norm, 1, nullptr, 0, c.eps, Rq, t, cq_, nullptr));
             DL_OP("op_linear", ggb_op_linear(dt_, w.uq, (int64_t)H * D, Rq, cq_, Rq, t, q_, (int64_t)H * D));
             DL_OP("op_attn_prep", ggb_op_latent_kv_store(dt_, pr_ + Rq, N, t, R, 0, 0, w.dkv_norm, c.eps, nullptr, pos0_, table, B, cache));
-            DL_OP("op_attn_prep", ggb_op_latent_q_absorb(dt_, q_, (int64_t)H * D, t, H, D, 0, 0, nullptr, pos0_, w.uk, R, A.scale, qa_));
-            DL_OP("op_attn", ggb_op_latent_attn_window(dt_, qa_, cache, table, B, pos0_, t, H, R, 0, A.window, ns, part_));
-            DL_OP("op_attn_out", ggb_op_latent_attn_out_gated(dt_, part_, ns, nullptr, w.uv, t, H, R, Dv, pr_ + Rq + R, N, ao_));
+            const int64_t first = A.window > 0 ? std::max<int64_t>(0, pos0 - A.window + 1) : 0, n_vis = pos0 + T - first;
+            if (kv_rows_ >= n_vis && materialise(A, T)) {
+                const int64_t ldkv = ggb_window_cache_ld(H, D, Dv);
+                DL_OP("op_attn_prep", ggb_op_latent_expand(dt_, cache, table, B, first, n_vis, R, 0, w.ukv, (int64_t)H * (D + Dv), crows_, kvf_, kv_, ldkv));
+                DL_OP("op_attn_prep", ggb_op_scale(q_, A.scale, t * H * D, q_));
+                DL_OP("op_attn", ggb_op_window_attn(dt_, q_, kv_, page_iota_, B, posrel_ + li, t, H, H, D, Dv, A.window, nullptr, ao_, nullptr));
+                DL_OP("op_attn_out", ggb_op_head_gate(dt_, ao_, t, H, Dv, pr_ + Rq + R, N));
+            } else {
+                DL_OP("op_attn_prep", ggb_op_latent_q_absorb(dt_, q_, (int64_t)H * D, t, H, D, 0, 0, nullptr, pos0_, w.uk, R, A.scale, qa_));
+                DL_OP("op_attn", ggb_op_latent_attn_window(dt_, qa_, cache, table, B, pos0_, t, H, R, 0, A.window, ns, part_));
+                DL_OP("op_attn_out", ggb_op_latent_attn_out_gated(dt_, part_, ns, nullptr, w.uv, t, H, R, Dv, pr_ + Rq + R, N, ao_));
+            }
             DL_OP("op_linear", ggb_op_linear(dt_, w.o, W, (int64_t)H * Dv, ao_, (int64_t)H * Dv, t, ya_, W));
         }
         // x += norm1b(mixer), and the norm in front of what reads x next, in one pass
@@ -485,6 +527,14 @@ int ditalorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
     DL_TRY(ggb_upload(ids_, p.tokens, (size_t)p.T * 4));
     DL_TRY(ggb_upload(pos0_, &pos0, 4));
     if (n_want) DL_TRY(ggb_upload(want_, want, (size_t)n_want * 4));
+    if (p.T > 1) { // the portion's position counted from the first one a latent layer's window shows (materialised form)
+        std::vector<int32_t> rel(cfg_.layers.size(), 0);
+        for (size_t li = 0; li < cfg_.layers.size(); li++) {
+            const dl_layer_cfg &l = cfg_.layers[li];
+            if (l.type == 1) rel[li] = (int32_t)(p.pos0 - (l.latent.window > 0 ? std::max<int64_t>(0, p.pos0 - l.latent.window + 1) : 0));
+        }
+        DL_TRY(ggb_upload(posrel_, rel.data(), rel.size() * 4));
+    }
     // splits of a latent layer's visible positions (the widest window bounds them): enough CTAs for a short portion, one
     // split once the tokens fill the GPU
     int64_t n_vis = 1;
@@ -514,7 +564,7 @@ int ditalorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
             if (sg.table == p.block_table_dev && sg.state == p.state_dev && sg.n_split == (int)ns && sg.n_want == n_want) g = sg.graph;
         if (!g) {
             DL_TRY(ggb_capture_begin());
-            const int rc = emit(1, (int)ns, p.block_table_dev, p.state_dev, n_want);
+            const int rc = emit(1, p.pos0, (int)ns, p.block_table_dev, p.state_dev, n_want);
             const int rc2 = ggb_capture_end(&g);
             if (rc) return rc;
             if (rc2) return fail(rc2, "ggb_capture_end");
@@ -526,7 +576,7 @@ int ditalorn_model::forward(const lm_portion &p, const int32_t *want, int n_want
         }
         DL_TRY(ggb_graph_launch(g));
     } else {
-        DL_TRY(emit(p.T, (int)ns, p.block_table_dev, p.state_dev, n_want));
+        DL_TRY(emit(p.T, p.pos0, (int)ns, p.block_table_dev, p.state_dev, n_want));
     }
     kernels_last_ = (int)(ggb_launch_count() - l0);
     return 0;

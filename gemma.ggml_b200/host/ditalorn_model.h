@@ -71,6 +71,7 @@ struct dl_layer_w {
     // latent attention
     float *dq_norm = nullptr, *dkv_norm = nullptr;
     void *uq = nullptr, *uk = nullptr, *uv = nullptr;
+    void *ukv = nullptr; // [W_uk; W_uv] stacked: keys and values of every head in one product (portions, materialised form)
     int cache_index = -1;
     // experts: [E][2 ff][W] (gate rows, then up rows), [E][W][ff]
     void *e_gate_up = nullptr, *e_down = nullptr;
@@ -110,7 +111,8 @@ class ditalorn_model : public lm_model {
     ditalorn_model() {}
     int load(const safetensors_file *file, uint64_t seed);
     int alloc_scratch();
-    int emit(int T, int n_split, const int32_t *table_dev, float *state, int n_want);
+    int emit(int T, int64_t pos0, int n_split, const int32_t *table_dev, float *state, int n_want);
+    bool materialise(const dl_latent_cfg &a, int T) const; // which form of the latent attention a portion of T tokens takes
     int upload_matrix(const std::vector<float> &host, void **dev);
     int upload_f32(const std::vector<float> &host, float **dev);
     int fail(int rc, const std::string &what);
@@ -131,6 +133,12 @@ class ditalorn_model : public lm_model {
     float *x_ = nullptr, *pr_ = nullptr, *cv_ = nullptr, *q_ = nullptr, *qa_ = nullptr, *part_ = nullptr, *sa_ = nullptr, *ya_ = nullptr,
           *gu_ = nullptr, *y2_ = nullptr, *route_w_ = nullptr, *route_z_ = nullptr, *xw_ = nullptr, *logits_ = nullptr, *cap_ = nullptr;
     void *h_ = nullptr, *cq_ = nullptr, *ao_ = nullptr, *act_ = nullptr, *hw_ = nullptr;
+    // the materialised form: gathered latents, keys | values of the visible range (fp32 scratch, then the storage type),
+    // an identity page table, the portion's position counted from the first visible one (per layer)
+    void *crows_ = nullptr, *kv_ = nullptr;
+    float *kvf_ = nullptr;
+    int32_t *page_iota_ = nullptr, *posrel_ = nullptr;
+    int64_t kv_rows_ = 0;
     int64_t part_rows_ = 0;
     bool capture_ = false, use_graphs_ = true;
     int cap_T_ = 0, kernels_last_ = 0;

@@ -388,6 +388,14 @@ int ggb_op_latent_attn_out(int dt, const float *part, int n_split, const float *
  * j <= i); the splits deal the tiles from the first visible one */
 int ggb_op_latent_attn_window(int dt, const float *qa, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0,
                               int64_t T, int H, int R, int Dr, int64_t window, int n_split, float *part);
+/* The materialised form, for portions whose window is short beside the latent: the latents of positions [first, first + n)
+ * are gathered (c_rows, dt [n][R]) and multiplied by w_ukv = [W_uk; W_uv] ([N][R], N = H (D + Dv)): kv (dt, row pitch ld_kv)
+ * holds rows [k (H D) | v (H Dv)], which ggb_op_window_attn reads as a cache of H key heads through an identity page table
+ * and positions counted from `first`.  kv_f32 ([n][ld_kv] fp32) is scratch for the bf16 type. */
+int ggb_op_latent_expand(int dt, const void *cache, const int32_t *block_table, int block_size, int64_t first, int64_t n, int R, int Dr,
+                         const void *w_ukv, int64_t N, void *c_rows, float *kv_f32, void *kv, int64_t ld_kv);
+/* x (dt, [T][H * Dv], in place): head h of token t times sigmoid(gate[t * ldg + h]) */
+int ggb_op_head_gate(int dt, void *x, int64_t T, int H, int Dv, const float *gate, int64_t ldg);
 /* the merge without a sink (sink NULL: ordinary soft-max over the keys) and / or with an output gate: head h of token t
  * is multiplied by sigmoid(gate[t * ldg + h]) (fp32 raw projections; gate NULL: none) */
 int ggb_op_latent_attn_out_gated(int dt, const float *part, int n_split, const float *sink, const void *w_uv, int64_t T, int H, int R, int Dv,
