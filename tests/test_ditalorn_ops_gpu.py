@@ -366,3 +366,68 @@ def test_experts_in_step_form_and_in_portion_form(gpu, dt, T):
     tol = 2e-2 if dt == BF16 else 5e-6
     assert F.rel_err(x.download(np.float32, T * W).reshape(T, W), x2) < tol
     assert F.rel_err(from_dt(dt, out, (T, W)), P.norm_centered(x2, wy.astype(np.float64), eps)) < tol
+
+
+# ------------------------------------------------------------------------------------------------ latent attention, materialised form
+def run_latent_materialised(gpu, dt, d, q, wuk, wuv, gate, nw, H, D, Dv, window, scale, cuts, page, eps=1e-5, seed=0):
+    """the portion form: kv_store, then per portion the visible latents expanded to keys | values by one product and read by
+    the window attention kernel through an identity page table, positions counted from the first visible one"""
+    T, R = d.shape
+    lib = gpu.cuda_lib()
+    ld = int(lib.ggb_latent_cache_ld(R, 0))
+    ldkv = int(lib.ggb_window_cache_ld(H, D, Dv))
+    n_pages = (T + page - 1) // page + 3
+    table = np.random.default_rng(seed).permutation(n_pages).astype(np.int32)
+    es = 2 if dt == BF16 else 4
+    cache, tb = zeros(gpu, n_pages * page * ld * es), dev(gpu, table)
+    ukv = dev(gpu, as_dt(dt, np.concatenate([wuk, wuv]))[1])
+    nwd, ident = dev(gpu, f32(nw)), dev(gpu, np.arange(T // page + 2, dtype=np.int32))
+    lo, got = 0, []
+    for c in cuts:
+        first = max(0, lo - window + 1) if window else 0
+        n = lo + c - first
+        pos0, rel = dev(gpu, np.array([lo], dtype=np.int32)), dev(gpu, np.array([lo - first], dtype=np.int32))
+        crows, kvf, kv, out = zeros(gpu, n * R * es), zeros(gpu, n * ldkv * 4), zeros(gpu, n * ldkv * es), zeros(gpu, c * H * Dv * es)
+        gpu.check(lib.ggb_op_latent_kv_store(dt, dev(gpu, f32(d[lo:lo + c])).ptr, R, c, R, 0, 0, nwd.ptr, eps, None, pos0.ptr, tb.ptr, page, cache.ptr), "kv_store")
+        gpu.check(lib.ggb_op_latent_expand(dt, cache.ptr, tb.ptr, page, first, n, R, 0, ukv.ptr, H * (D + Dv), crows.ptr, kvf.ptr, kv.ptr, ldkv), "expand")
+        qs = dev(gpu, f32(q[lo:lo + c] * scale))
+        gpu.check(lib.ggb_op_window_attn(dt, qs.ptr, kv.ptr, ident.ptr, page, rel.ptr, c, H, H, D, Dv, window or 0, None, out.ptr, None), "window_attn")
+        if gate is not None:
+            gpu.check(lib.ggb_op_head_gate(dt, out.ptr, c, H, Dv, dev(gpu, f32(gate[lo:lo + c])).ptr, H), "head_gate")
+        got.append(from_dt(dt, out, (c, H * Dv)))
+        lo += c
+    return np.concatenate(got)
+
+
+@pytest.mark.parametrize("dt", [F32, BF16])
+@pytest.mark.parametrize("H,D,Dv,R,window,page", [(2, 6, 4, 20, 5, 4), (4, 32, 32, 64, 70, 16), (3, 8, 6, 40, None, 16), (1, 4, 2, 9, 1, 8)])
+def test_latent_attention_materialised_form_equals_the_oracle(gpu, dt, H, D, Dv, R, window, page):
+    r = np.random.default_rng(H * 10 + R)
+    T = 150
+    d, q, gate = r.standard_normal((T, R)), r.standard_normal((T, H * D)), 2 * r.standard_normal((T, H))
+    wuk, wuv, nw = r.standard_normal((H * D, R)) / np.sqrt(R), r.standard_normal((H * Dv, R)) / np.sqrt(R), 1 + 0.2 * r.standard_normal(R)
+    want = latent_want(dt, d, q, wuk, wuv, gate, nw, H, D, Dv, window, 0.5)
+    for cuts in ([T], [40, 33, 77], [32, 32, 32, 54]):
+        got = run_latent_materialised(gpu, dt, d, q, wuk, wuv, gate, nw, H, D, Dv, window, 0.5, cuts, page)
+        assert F.rel_err(got, want) < (3e-2 if dt == BF16 else 5e-6), cuts
+
+
+@pytest.mark.parametrize("dt", [F32, BF16])
+def test_latent_materialised_window_edge_with_one_key_standing_out(gpu, dt):
+    H, D, Dv, R, page = 2, 8, 6, 16, 16
+    T = 200
+    r = np.random.default_rng(6)
+    wuk = np.concatenate([np.eye(D, R), r.standard_normal((D, R)) / 3])
+    wuv, nw = r.standard_normal((H * Dv, R)), np.ones(R)
+    for window, i, j in ((32, 199, 168), (32, 199, 167), (17, 64, 48), (17, 64, 47), (70, 199, 130), (70, 199, 129), (200, 199, 0), (33, 96, 64), (33, 96, 63),
+                         (None, 199, 0), (40, 130, 100), (40, 140, 100)):
+        d, q = 0.3 * r.standard_normal((T, R)), 0.05 * r.standard_normal((T, H * D))
+        d[:, R - 1] += 4.0
+        u = np.zeros(R); u[j % D] = 1.0
+        d[j] = 50.0 * u
+        q[i, :D] = 12.0 * u[:D]
+        want = latent_want(dt, d, q, wuk, wuv, None, nw, H, D, Dv, window, 1.0)
+        for cuts in ([T], [100, 100], [64, 36, 100]):  # the key and the query in one portion, and in two
+            got = run_latent_materialised(gpu, dt, d, q, wuk, wuv, None, nw, H, D, Dv, window, 1.0, cuts, page, seed=i)
+            assert np.abs(got[i] - want[i]).max() < (5e-2 if dt == BF16 else 2e-5), (window, i, j, cuts)
+            assert F.rel_err(got, want) < (3e-2 if dt == BF16 else 5e-6), (window, i, j, cuts)
