@@ -937,7 +937,11 @@ def run_ditalorn(args):
         lin_params = n_att * (W * (H * D + 2 * Gk * D) + W * H * D) + n_lat * (W * (Rq + R + H) + Rq * H * D + W * H * D)
         lin_flops, lin_bytes = 2.0 * T * lin_params + 2.0 * V * W, 2.0 * (lin_params + V * W)
         sig_flops = 4.0 * n_att * H * D * vis_all                # q.k and p.v
-        lat_flops = 4.0 * n_lat * H * R * vis_win                # the absorbed form: qa.c and p.c, R numbers each
+        # portions take the materialised form when heads are short beside the latent (q.k and p.v over D numbers each, after
+        # one product [visible][R] x [H 2D][R]^T per portion); else the absorbed form (qa.c and p.c, R numbers each)
+        materialised = 4 * 2 * D <= 5 * R
+        vis_rows = sum(min(p0 + 1024, win + 1024 - 1) for p0 in range(0, T, 1024))
+        lat_flops = n_lat * (4.0 * H * D * vis_win + 2.0 * vis_rows * R * 2 * H * D) if materialised else 4.0 * n_lat * H * R * vis_win
         moe_flops = 2.0 * T * top * 3 * eff * W * nl
         moe_bytes = 2.0 * top * 3 * eff * W * nl
         sig_cache, lat_cache = 2.0 * n_att * ctx * 2 * Gk * D, 2.0 * n_lat * min(ctx, win) * R
@@ -949,7 +953,8 @@ def run_ditalorn(args):
                         "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
                         "moe_linear_tflops": moe_flops / (pf_ops["op_moe_linear"] / 1e3) / 1e12,
                         "sigmoid_attn_tflops_cuda_cores": sig_flops / (pf_ops["op_sigmoid_attn"] / 1e3) / 1e12,
-                        "latent_attn_tflops_cuda_cores": lat_flops / (pf_ops["op_attn"] / 1e3) / 1e12},
+                        "latent_attn_form": "materialised" if materialised else "absorbed",
+                        "latent_attn_tflops": lat_flops / ((pf_ops["op_attn"] + (pf_ops["op_attn_prep"] if materialised else 0.0)) / 1e3) / 1e12},
             "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
                        "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
                        "moe_linear_gbs": moe_bytes / (dc_ops["op_moe_linear"] / 1e3) / 1e9,

@@ -110,15 +110,14 @@ template <typename E> struct RowVec { // 16 bytes of a cache row
 };
 
 // what a head's weighted sum becomes: divided by the soft-max sum, turned back by the reader's position, stored
-template <typename E>
+template <typename E, int NP = kMaxDvRegs / 2>
 __device__ __forceinline__ void window_finish(const float *acc, float l, int64_t i, int lane, int Dv, const float *__restrict__ cs_v, E *orow) {
-    const int nreg = (Dv + 63) / 64;
     const float inv = 1.0f / l;
     const float *cv = cs_v ? cs_v + i * (Dv / 2) * 2 : nullptr;
 #pragma unroll
-    for (int r = 0; r < kMaxDvRegs / 2; r++) {
+    for (int r = 0; r < NP; r++) {
         const int c = 2 * lane + 64 * r;
-        if (r < nreg && c < Dv) {
+        if (c < Dv) {
             float u = acc[2 * r] * inv, w = acc[2 * r + 1] * inv;
             if (cv) { // turned back: by -i
                 const float cs = cv[c], sn = cv[c + 1];
@@ -294,13 +293,16 @@ __global__ void __launch_bounds__(32) window_merge_kernel(const float *__restric
 // ---- portions: 32 tokens of one head per CTA, tiles of 32 cache rows staged in shared memory
 constexpr int kQT = 32, kQPW = kQT / kWarps; // queries per CTA and per warp
 
-template <typename E>
+// NP: groups of 64 value coordinates (a pair per lane) the lanes accumulate, Dv <= 64 NP.  VEC: rows are staged and K rows
+// read in 16-byte pieces; the K pitch kp is then a multiple of 4 words with kp / 4 odd (the eight lanes of a quarter warp, a
+// row each, cover all 32 banks) and the V pitch vp a multiple of 4; otherwise kp is odd and vp even (float2 reads).
+template <typename E, int NP, bool VEC>
 __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                        const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
-                                                                       int64_t T, int H, int G, int D, int Dv, int64_t window,
-                                                                       const float *__restrict__ cs_v, E *__restrict__ out, int vec) {
+                                                                       int64_t T, int H, int G, int D, int Dv, int kp, int vp, int64_t window,
+                                                                       const float *__restrict__ cs_v, E *__restrict__ out) {
     extern __shared__ __align__(16) float wa_smem[];
-    const int Dp = (D + 3) & ~3, kp = D | 1, vp = Dv + 2; // pitches in words: q rows 16-byte aligned, K rows odd, V rows even (float2 reads)
+    const int Dp = (D + 3) & ~3;
     float *sq = wa_smem;              // [kQT][Dp]
     float *sk = sq + kQT * Dp;        // [32][kp]
     float *sv = sk + 32 * kp;         // [32][vp]
@@ -315,14 +317,13 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
         sq[e] = (qi < nq && d < D) ? q[((t0 + qi) * H + h) * D + d] : 0.f;
     }
     const int64_t jlo = window > 0 ? max((int64_t)0, i0 - window + 1) : 0;
-    const int nreg = (Dv + 63) / 64;
-    float acc[kQPW][kMaxDvRegs], m[kQPW], l[kQPW];
+    float acc[kQPW][2 * NP], m[kQPW], l[kQPW];
 #pragma unroll
     for (int a = 0; a < kQPW; a++) {
         m[a] = -INFINITY;
         l[a] = 0.f;
 #pragma unroll
-        for (int r = 0; r < kMaxDvRegs; r++) acc[a][r] = 0.f;
+        for (int r = 0; r < 2 * NP; r++) acc[a][r] = 0.f;
     }
     const int64_t koff = (int64_t)g * D, voff = (int64_t)G * D + (int64_t)g * Dv;
     const int row_elems = D + Dv;
@@ -334,7 +335,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
         for (int rr = warp; rr < 32; rr += kWarps) {
             const int64_t j = j0 + min(rr, n_rows - 1); // a row past the last one repeats it (masked below, weight 0)
             const E *row = cache + ((int64_t)table[j / B] * B + j % B) * cache_ld;
-            if (vec) {
+            if (VEC) {
                 constexpr int VN = RowVec<E>::n;
                 const int nk = D / VN, nv = Dv / VN;
                 for (int vi = lane; vi < nk + nv; vi += 32) {
@@ -342,9 +343,9 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
                     const int c = (is_k ? vi : vi - nk) * VN;
                     RowVec<E> x;
                     x.raw = *reinterpret_cast<const uint4 *>(row + (is_k ? koff : voff) + c);
-                    float *dst = is_k ? sk + rr * kp + c : sv + rr * vp + c;
+                    float4 *dst = reinterpret_cast<float4 *>(is_k ? sk + rr * kp + c : sv + rr * vp + c);
 #pragma unroll
-                    for (int u = 0; u < VN; u++) dst[u] = x.at(u);
+                    for (int u = 0; u < VN; u += 4) dst[u / 4] = make_float4(x.at(u), x.at(u + 1), x.at(u + 2), x.at(u + 3));
                 }
             } else {
                 for (int c = lane; c < row_elems; c += 32) {
@@ -362,7 +363,13 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
         const int D4 = D & ~3;
 #pragma unroll 2
         for (int d = 0; d < D4; d += 4) {
-            const float k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
+            float k0, k1, k2, k3;
+            if (VEC) {
+                const float4 kv = *reinterpret_cast<const float4 *>(kr + d);
+                k0 = kv.x, k1 = kv.y, k2 = kv.z, k3 = kv.w;
+            } else {
+                k0 = kr[d], k1 = kr[d + 1], k2 = kr[d + 2], k3 = kr[d + 3];
+            }
 #pragma unroll
             for (int a = 0; a < kQPW; a++) {
                 const float4 qv = *reinterpret_cast<const float4 *>(sq + (warp * kQPW + a) * Dp + d);
@@ -389,17 +396,18 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
             p[a] = vis ? expf(sa - m_new) : 0.f;
             l[a] = l[a] * corr + warp_sum_f32(p[a]);
 #pragma unroll
-            for (int r = 0; r < kMaxDvRegs; r++) acc[a][r] *= corr;
+            for (int r = 0; r < 2 * NP; r++) acc[a][r] *= corr;
             m[a] = m_new;
         }
+#pragma unroll 2
         for (int jj = 0; jj < n_rows; jj++) {
             float pj[kQPW];
 #pragma unroll
             for (int a = 0; a < kQPW; a++) pj[a] = __shfl_sync(0xffffffffu, p[a], jj);
 #pragma unroll
-            for (int r = 0; r < kMaxDvRegs / 2; r++) {
+            for (int r = 0; r < NP; r++) {
                 const int c = 2 * lane + 64 * r;
-                if (r < nreg && c < Dv) {
+                if (c < Dv) {
                     const float2 vv = *reinterpret_cast<const float2 *>(sv + jj * vp + c);
 #pragma unroll
                     for (int a = 0; a < kQPW; a++) {
@@ -414,7 +422,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
     for (int a = 0; a < kQPW; a++) {
         const int qi = warp * kQPW + a;
         if (qi >= nq) continue;
-        window_finish(acc[a], l[a], i0 + qi, lane, Dv, cs_v, out + ((t0 + qi) * H + h) * Dv);
+        window_finish<E, NP>(acc[a], l[a], i0 + qi, lane, Dv, cs_v, out + ((t0 + qi) * H + h) * Dv);
     }
 }
 
@@ -461,17 +469,36 @@ int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t 
     const int vec = D % vn == 0 && ((uintptr_t)cache % 16 == 0); // rows are 8 numbers apart at least: 16-byte aligned in both types
     cudaStream_t st = ggb_cuda_stream();
     if (T >= kQT) { // a portion: tiles of cache rows staged once for 32 queries
-        const size_t smem = ((size_t)kQT * Dp + 32 * (size_t)(D | 1) + 32 * (size_t)(Dv + 2)) * 4;
+        // 16-byte pieces need every head's keys and values to start on one: D, Dv and G * D whole pieces
+        const bool tv = vec && Dv % vn == 0 && ((int64_t)G * D) % vn == 0;
+        int kp = D | 1, vp = Dv + 2;
+        if (tv) {
+            kp = (D + 3) & ~3;
+            if ((kp / 4) % 2 == 0) kp += 4;
+            vp = (Dv + 3) & ~3;
+        }
+        const size_t smem = ((size_t)kQT * Dp + 32 * (size_t)kp + 32 * (size_t)vp) * 4;
         GGB_CHECK_ARG(smem <= 200 * 1024, "window_attn: head sizes %d / %d do not fit shared memory", D, Dv);
         const dim3 grid((unsigned)((T + kQT - 1) / kQT), (unsigned)H);
-#define WT_LAUNCH(ET)                                                                                                        \
+#define WT_LAUNCH(ET, NP, VEC)                                                                                               \
     {                                                                                                                        \
-        auto kfn = window_attn_tile_kernel<ET>;                                                                              \
+        auto kfn = window_attn_tile_kernel<ET, NP, VEC>;                                                                     \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
-        kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window, \
-                                             cos_sin_v, (ET *)out, vec && Dv % vn == 0);                                     \
+        kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, kp, vp, \
+                                             window, cos_sin_v, (ET *)out);                                                  \
     }
-        if (dt == GGB_TYPE_BF16) WT_LAUNCH(__nv_bfloat16) else WT_LAUNCH(float)
+#define WT_NP(ET, VEC)                             \
+    {                                              \
+        if (Dv <= 64) WT_LAUNCH(ET, 1, VEC)        \
+        else if (Dv <= 128) WT_LAUNCH(ET, 2, VEC)  \
+        else WT_LAUNCH(ET, 4, VEC)                 \
+    }
+        if (dt == GGB_TYPE_BF16) {
+            if (tv) WT_NP(__nv_bfloat16, true) else WT_NP(__nv_bfloat16, false)
+        } else {
+            if (tv) WT_NP(float, true) else WT_NP(float, false)
+        }
+#undef WT_NP
 #undef WT_LAUNCH
     } else {
         const size_t smem = (size_t)kWarps * Dp * 4 + (size_t)kWarps * kPartW * 4;
