@@ -64,7 +64,7 @@ int dl_parse_config(const json_value &j, const safetensors_file *file, dl_config
             a.kv_heads = (int)m->integer("kv_heads", a.heads);
             a.dim = (int)m->integer("dim", a.heads > 0 ? shape_of(p + "q", 0) / a.heads : 0);
             a.vdim = (int)m->integer("vdim", a.kv_heads > 0 && shape_of(p + "v", 0) ? shape_of(p + "v", 0) / a.kv_heads : a.dim);
-            a.conv = (int)m->integer("conv", std::max<long long>(1, shape_of(p + "q.conv", 1)));
+            a.conv = (int)m->integer("conv", shape_of(p + "q.conv", 1));
             a.scale = (float)m->number("scale", 1.0);
             if (const json_value *t = m->get("q_temp")) {
                 a.temp_coef = (float)t->number("coef", 0.0);
@@ -73,7 +73,7 @@ int dl_parse_config(const json_value &j, const safetensors_file *file, dl_config
             }
             if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0)
                 return bad(where + "sizes must be positive and kv_heads must divide heads");
-            if (a.conv < 1 || a.conv > 8) return bad(where + "conv must be between 1 and 8 taps");
+            if (a.conv < 0 || a.conv > 8) return bad(where + "conv must have at most 8 taps");
             if (a.vdim > 256) return bad(where + "vdim above 256 is not built");
         } else if (type == "latent_attention") {
             l.type = 1;
@@ -205,7 +205,7 @@ int ditalorn_model::load(const safetensors_file *file, uint64_t seed) {
             DL_GET(m + "v.b", 1, GV, 0.2f, 0.f, &a);
             bias.insert(bias.end(), a.begin(), a.end());
             DL_TRY(upload_f32(bias, &w.proj_b));
-            if (A.conv > 1) { // the three convolutions side by side, as their channels lie in the stacked product
+            if (A.conv >= 1) { // the three convolutions side by side, as their channels lie in the stacked product
                 DL_GET(m + "q.conv", HD, A.conv, 0.5f, 0.f, &a);
                 cw.insert(cw.end(), a.begin(), a.end());
                 DL_GET(m + "k.conv", GD, A.conv, 0.5f, 0.f, &a);
@@ -214,7 +214,7 @@ int ditalorn_model::load(const safetensors_file *file, uint64_t seed) {
                 cw.insert(cw.end(), a.begin(), a.end());
                 w.s_tail = st;
                 st += ((int64_t)(A.conv - 1) * C + 3) / 4 * 4;
-            } else { // one tap of weight one: the biased projection as it is
+            } else { // no convolution: one tap of weight one, the biased projection as it is
                 cw.assign((size_t)C, 1.0f);
             }
             DL_TRY(upload_f32(cw, &w.conv));
@@ -449,7 +449,7 @@ int ditalorn_model::emit(int T, int64_t pos0, int ns, const int32_t *table, floa
         if (l.type == 0) {
             const dl_attn_cfg &A = l.attn;
             const int64_t HD = (int64_t)A.heads * A.dim, GD = (int64_t)A.kv_heads * A.dim, GV = (int64_t)A.kv_heads * A.vdim, C = HD + GD + GV;
-            DL_OP("op_conv", ggb_op_causal_conv_bias(dt_, pr_, N, t, C, w.conv, w.proj_b, A.conv, 0, 0, A.conv > 1 ? state + w.s_tail : nullptr, cv_, C,
+            DL_OP("op_conv", ggb_op_causal_conv_bias(dt_, pr_, N, t, C, w.conv, w.proj_b, std::max(A.conv, 1), 0, 0, A.conv > 1 ? state + w.s_tail : nullptr, cv_, C,
                                                      nullptr));
             DL_OP("op_attn_prep", ggb_op_sigmoid_qkv_store(dt_, cv_, cv_ + HD, cv_ + HD + GD, C, t, A.heads, A.kv_heads, A.dim, A.vdim, A.temp_coef,
                                                            A.temp_every, c.eps, A.scale, pos0_, table, B, cache, q_));

@@ -28,7 +28,7 @@
 
 struct dl_attn_cfg { // "attention"
     int heads = 0, kv_heads = 0, dim = 0, vdim = 0;
-    int conv = 1;          // taps; 1: no convolution
+    int conv = 0;          // taps; 0: no convolution
     int temp_every = 0;    // 0: no query temperature
     float temp_coef = 0.f, scale = 1.f;
 };

@@ -34,6 +34,7 @@ def test_config_reader_takes_every_size_from_the_file(G):
     (lambda c: c["layers"][0].update(type="other_mixer"), "unknown mixer"),
     (lambda c: c["layers"][1]["mixer"].update(kv_heads=3), "kv_heads must divide"),
     (lambda c: c["layers"][1]["mixer"].update(conv=12), "conv"),
+    (lambda c: c["layers"][1]["mixer"].update(conv=-1), "conv"),
     (lambda c: c["layers"][1]["mixer"]["q_temp"].update(every=0), "q_temp.every"),
     (lambda c: c["layers"][0]["mixer"].update(kv_rank=0), "positive"),
     (lambda c: c["layers"][0]["mlp"].update(kind="dense"), "unknown mlp"),

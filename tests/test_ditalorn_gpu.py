@@ -141,7 +141,8 @@ OTHER = {
         [F.attention(heads=1, kv_heads=1, dim=4, vdim=4, conv=8, every=1, mlp=F.moe(ff=4, experts=1, top=1, count=1, keep=1)),
          F.latent(heads=1, dim=4, vdim=4, kv_rank=4, q_rank=4, window=1, mlp=F.moe(ff=4, experts=4, top=4, count=4, keep=4))], vocab=7, width=4, scale=1.0),
     "attention only, as many key heads as heads, odd sizes": F.config(
-        [F.attention(heads=5, kv_heads=5, dim=7, vdim=3, conv=2, mlp=None), F.attention(heads=2, kv_heads=1, dim=9, vdim=33, conv=5, every=3, mlp=F.moe(experts=9, top=2, count=3, keep=1))],
+        [F.attention(heads=5, kv_heads=5, dim=7, vdim=3, conv=2, mlp=None), F.attention(heads=2, kv_heads=1, dim=9, vdim=33, conv=5, every=3, mlp=F.moe(experts=9, top=2, count=3, keep=1)),
+         F.attention(heads=3, kv_heads=1, dim=4, vdim=6, conv=1, every=0, mlp=None)],
         vocab=31, width=22),
     "latent only, a window longer than the prompt and none": F.config(
         [F.latent(heads=4, dim=6, vdim=5, kv_rank=9, q_rank=17, window=300), F.latent(heads=2, dim=16, vdim=16, kv_rank=40, q_rank=8, window=0, mlp=None)], vocab=40, width=24),
