@@ -645,6 +645,16 @@ int ggb_op_norm_gate(int dt, const float *o, int64_t ldo, const float *gate, int
 // ------------------------------------------------------------------------------------------------ learned positions, norms on both sides of a sublayer
 namespace {
 
+__device__ __forceinline__ float block_sum_any(float v, float *red) { // all threads get the sum; blockDim.x a multiple of 32, at most 1024
+    v = warp_sum_f32(v);
+    __syncthreads(); // `red` may still be read by the previous call
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) tot += red[i];
+    return tot;
+}
+
 // one CTA per token: the embedding row times `scale` plus the (unscaled) row of the token's position
 template <typename E>
 __global__ void __launch_bounds__(256) embed_pos_kernel(const E *__restrict__ table, const E *__restrict__ pos_table, const int32_t *__restrict__ ids,
@@ -673,12 +683,12 @@ constexpr int kMaxCombine = GGB_MOE_COMBINE_NORM_MAX_TOP;
 // With inv / wt the sublayer's output is gathered on the way in: v = sum_k wt[t][k] a[inv[t][k]] over the `top` expert
 // slots of the token, added in slot order (what moe_combine_kernel computes).
 template <typename E>
-__global__ void __launch_bounds__(256) norm_add_norm_kernel(const float *__restrict__ a, const float *__restrict__ bias,
+__global__ void __launch_bounds__(1024) norm_add_norm_kernel(const float *__restrict__ a, const float *__restrict__ bias,
                                                             const int32_t *__restrict__ inv, const float *__restrict__ wt, int top,
                                                             const float *__restrict__ wa, float eps, int64_t n, float *x,
                                                             const float *__restrict__ wy, E *__restrict__ y) {
     extern __shared__ float nn_row[];
-    __shared__ float red[8];
+    __shared__ float red[32];
     __shared__ float s_wt[kMaxCombine];
     __shared__ int64_t s_off[kMaxCombine];
     const int64_t t = blockIdx.x;
@@ -703,7 +713,7 @@ __global__ void __launch_bounds__(256) norm_add_norm_kernel(const float *__restr
         nn_row[i] = v;
         ss = fmaf(v, v, ss);
     }
-    const float ra = 1.0f / sqrtf(block_sum_256(ss, red) / (float)n + eps);
+    const float ra = 1.0f / sqrtf(block_sum_any(ss, red) / (float)n + eps);
     ss = 0.f;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { // a thread reads back what it wrote itself
         const float v = x[t * n + i] + nn_row[i] * ra * wa[i];
@@ -712,7 +722,7 @@ __global__ void __launch_bounds__(256) norm_add_norm_kernel(const float *__restr
         ss = fmaf(v, v, ss);
     }
     if (!y) return;
-    const float rx = 1.0f / sqrtf(block_sum_256(ss, red) / (float)n + eps);
+    const float rx = 1.0f / sqrtf(block_sum_any(ss, red) / (float)n + eps);
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) y[t * n + i] = from_f32<E>(nn_row[i] * rx * wy[i]);
 }
 
@@ -749,11 +759,13 @@ int ggb_norm_add_norm_launch(int dt, const float *a, const float *bias, const in
     GGB_CHECK_ARG(a && wa && x && E > 0 && T > 0 && (!y || wy) && (!inv || (wt && top > 0 && top <= kMaxCombine)), "norm_add_norm: bad arguments");
     const size_t smem = (size_t)E * 4;
     GGB_CHECK_ARG(smem <= 200 * 1024, "norm_add_norm: width %lld does not fit shared memory", (long long)E);
+    // a step of few tokens is a chain of latencies on a nearly empty GPU: a wide CTA shortens every pass over the row
+    const unsigned threads = T <= 64 && E >= 2048 ? 1024 : T <= 64 && E >= 1024 ? 512 : 256;
 #define NN_LAUNCH(ET)                                                                                                         \
     {                                                                                                                          \
         auto k = norm_add_norm_kernel<ET>;                                                                                     \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
-        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(a, bias, inv, wt, top, wa, eps, E, x, wy, (ET *)y);                                  \
+        k<<<(unsigned)T, threads, smem, ggb_cuda_stream()>>>(a, bias, inv, wt, top, wa, eps, E, x, wy, (ET *)y);                                  \
     }
     if (dt == GGB_TYPE_BF16) NN_LAUNCH(__nv_bfloat16) else NN_LAUNCH(float)
 #undef NN_LAUNCH

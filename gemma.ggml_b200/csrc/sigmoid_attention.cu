@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_step_kernel(const fl
             float a0 = 0.f, a1 = 0.f;
             if (vec) {
                 constexpr int VN = RowVec<E>::n;
-#pragma unroll 8
+#pragma unroll 16
                 for (int d = 0; d < D; d += VN) {
                     RowVec<E> kv;
                     kv.raw = *reinterpret_cast<const uint4 *>(kr + d);
@@ -114,13 +114,14 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_step_kernel(const fl
             p = sigmoid_f32((a0 + a1) - penalty_f32(hr1, hr2, i - j) + hpb);
         }
         const int n_keys = (int)min((int64_t)32, i - j0 + 1);
-        // rows in groups of 8: their loads are independent and in flight together (a row past the last visible one
+        // rows in groups of 16: their loads are independent and in flight together (a row past the last visible one
         // repeats it with weight 0)
-        for (int jb = 0; jb < n_keys; jb += 8) {
-            const E *vrow[8];
-            float pj[8];
+        constexpr int kRows = 16;
+        for (int jb = 0; jb < n_keys; jb += kRows) {
+            const E *vrow[kRows];
+            float pj[kRows];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < kRows; u++) {
                 const int jj = min(jb + u, n_keys - 1);
                 pj[u] = jb + u < n_keys ? __shfl_sync(0xffffffffu, p, jj) : 0.f;
                 vrow[u] = cache + __shfl_sync(0xffffffffu, my_row, jj) * cache_ld + voff;
@@ -129,11 +130,11 @@ __global__ void __launch_bounds__(32 * kWarps) sigmoid_attn_step_kernel(const fl
             for (int r = 0; r < kMaxDvRegs; r++) {
                 const int c = lane + 32 * r;
                 if (c < Dv) {
-                    float vv[8];
+                    float vv[kRows];
 #pragma unroll
-                    for (int u = 0; u < 8; u++) vv[u] = to_f32(vrow[u][c]);
+                    for (int u = 0; u < kRows; u++) vv[u] = to_f32(vrow[u][c]);
 #pragma unroll
-                    for (int u = 0; u < 8; u++) acc[r] = fmaf(pj[u], vv[u], acc[r]);
+                    for (int u = 0; u < kRows; u++) acc[r] = fmaf(pj[u], vv[u], acc[r]);
                 }
             }
         }
