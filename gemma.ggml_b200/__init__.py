@@ -170,6 +170,15 @@ _CUDA_SIG = {
     "ggb_op_sigmoid_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, f32, i32, f32, f32, vp, vp, i32, vp, vp]),
     "ggb_sigmoid_attn_scratch_bytes": (sz, [i32]),
     "ggb_op_sigmoid_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp]),
+    "ggb_op_masked_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, f32, i32, i32, vp, vp, f32, vp, vp, i32, vp, vp]),
+    "ggb_op_masked_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, i32, f32, vp, vp, vp]),
+    "ggb_op_channel_delta": (i32, [vp, vp, vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, i64]),
+    "ggb_op_moe_route_softmax": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp, vp, vp]),
+    "ggb_op_moe_group_identity": (i32, [vp, i64, i32, i32, i32, vp]),
+    "ggb_op_moe_linear_identity": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, i32, vp, i32, f32, f32, vp, i64]),
+    "ggb_op_moe_combine_identity": (i32, [i32, vp, vp, vp, vp, i64, i32, i32, i32, i64, vp, vp]),
+    "ggb_op_hyper_mix": (i32, [i32, vp, vp, vp, vp, vp, i32, vp, vp, f32, i64, i64, vp, vp, vp]),
+    "ggb_op_act_rows": (i32, [i32, vp, i64, i64, i64, i32, vp]),
     "ggb_comm_unique_id": (i32, [vp]), "ggb_comm_init": (i32, [vp, i32, i32]), "ggb_comm_destroy": (i32, []),
     "ggb_comm_rank": (i32, []), "ggb_comm_size": (i32, []), "ggb_op_allgather": (i32, [vp, vp, sz]),
 }
@@ -210,6 +219,7 @@ _HOST_SIG = {
     "sf_config_probe": (i32, [C.c_char_p, P(i64)]),
     "bg_config_probe": (i32, [C.c_char_p, P(i64)]),
     "dl_config_probe": (i32, [C.c_char_p, P(i64)]),
+    "kb_config_probe": (i32, [C.c_char_p, P(i64)]),
     "st_probe": (i32, [C.c_char_p, C.c_char_p, P(i64), P(i64), C.c_char_p, i32, P(i64)]),
     "mul_mat": (None, [i64, i64, i64, i64, i64, i64, i64, sz, i64, vp, vp, vp, vp, i32, vp]),
     "init_cuda_offload": (i32, [i32]),

@@ -772,3 +772,127 @@ int ggb_norm_add_norm_launch(int dt, const float *a, const float *bias, const in
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ several residual streams, plain activations
+namespace {
+
+constexpr int kMaxStreams = 16;
+
+// One CTA per row.  The residual is S streams x_1 .. x_S per token ([T][S][W] fp32).  In one pass over the token's columns:
+//   x0:   every stream starts as the row of x0 (the embedding output) instead of what xs holds
+//   y:    the sublayer's output enters, all streams at once from the old ones: x_t <- sum_s mix[s][t] x_s + coef[t] y
+//   in_w: u = sum_s in_w[s] x_s is read out, as fp32 (u_out) and / or normed, u / sqrt(mean(u^2) + eps) * nw, in dt (h)
+// With `rows` the CTA's token is rows[blockIdx.x] and nothing is written back to xs (a few rows read out at the end: what y
+// brings enters on the way).
+template <typename E, int SM>
+__global__ void __launch_bounds__(256) hyper_mix_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y,
+                                                        const float *__restrict__ mix, const float *__restrict__ coef, int S,
+                                                        const float *__restrict__ in_w, const float *__restrict__ nw, float eps, int64_t W,
+                                                        const int32_t *__restrict__ rows, float *__restrict__ u_out, E *__restrict__ h) {
+    extern __shared__ float hm_row[]; // [W] the read-out u
+    __shared__ float red[8], s_mix[SM * SM], s_coef[SM], s_in[SM];
+    const int64_t b = blockIdx.x, t = rows ? rows[b] : b;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[(i / S) * SM + i % S] = mix ? mix[i] : 0.f;
+    if ((int)threadIdx.x < S) {
+        s_coef[threadIdx.x] = coef ? coef[threadIdx.x] : 0.f;
+        s_in[threadIdx.x] = in_w ? in_w[threadIdx.x] : 0.f;
+    }
+    __syncthreads();
+    float *xr = xs + t * S * W;
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < W; i += blockDim.x) {
+        float x[SM];
+#pragma unroll
+        for (int s = 0; s < SM; s++) x[s] = s < S ? (x0 ? x0[t * W + i] : xr[s * W + i]) : 0.f;
+        if (y) {
+            const float yv = y[t * W + i];
+            float n[SM];
+#pragma unroll
+            for (int d = 0; d < SM; d++) {
+                float a = 0.f;
+#pragma unroll
+                for (int s = 0; s < SM; s++)
+                    if (s < S) a = fmaf(s_mix[s * SM + d], x[s], a);
+                n[d] = fmaf(s_coef[d], yv, a);
+            }
+#pragma unroll
+            for (int s = 0; s < SM; s++) x[s] = n[s];
+        }
+        if ((y || x0) && !rows) {
+#pragma unroll
+            for (int s = 0; s < SM; s++)
+                if (s < S) xr[s * W + i] = x[s];
+        }
+        if (in_w) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < SM; s++)
+                if (s < S) u = fmaf(s_in[s], x[s], u);
+            if (u_out) u_out[b * W + i] = u;
+            if (h) {
+                hm_row[i] = u;
+                ss = fmaf(u, u, ss);
+            }
+        }
+    }
+    if (!h) return;
+    const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)W + eps);
+    for (int64_t i = threadIdx.x; i < W; i += blockDim.x) h[b * W + i] = from_f32<E>(hm_row[i] * r * nw[i]); // a thread reads what it wrote
+}
+
+// y (dt, dense [T][F]) = act(x) for fp32 rows of stride ldx; act 0: as it is, 1: the square of relu
+template <typename E>
+__global__ void act_rows_kernel(const float *__restrict__ x, int64_t ldx, int64_t T, int64_t F, int act, E *__restrict__ y) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * F) return;
+    const int64_t t = i / F, f = i - t * F;
+    float v = x[t * ldx + f];
+    if (act == 1) v = v > 0.f ? v * v : 0.f;
+    y[i] = from_f32<E>(v);
+}
+
+} // namespace
+
+extern "C" {
+
+int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const float *mix, const float *coef, int S, const float *in_w,
+                     const float *nw, float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(xs && W > 0 && T > 0 && S > 0 && S <= kMaxStreams, "hyper_mix: bad arguments (%d streams, at most %d)", S, kMaxStreams);
+    GGB_CHECK_ARG((!y || (mix && coef)) && (!(u_out || h) || in_w) && (!h || nw), "hyper_mix: an input without its weights");
+    const size_t smem = h ? (size_t)W * 4 : 0;
+    GGB_CHECK_ARG(smem <= 200 * 1024, "hyper_mix: width %lld does not fit shared memory", (long long)W);
+#define HM_LAUNCH(ET, SM)                                                                                                     \
+    {                                                                                                                          \
+        auto k = hyper_mix_kernel<ET, SM>;                                                                                     \
+        if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
+        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h);      \
+    }
+#define HM_S(ET)                              \
+    {                                         \
+        if (S == 1) HM_LAUNCH(ET, 1)          \
+        else if (S == 2) HM_LAUNCH(ET, 2)     \
+        else if (S <= 4) HM_LAUNCH(ET, 4)     \
+        else if (S <= 8) HM_LAUNCH(ET, 8)     \
+        else HM_LAUNCH(ET, 16)                \
+    }
+    if (dt == GGB_TYPE_BF16) HM_S(__nv_bfloat16) else HM_S(float)
+#undef HM_S
+#undef HM_LAUNCH
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(x && y && T > 0 && F > 0 && ldx >= F && (act == 0 || act == 1), "act_rows: bad arguments");
+    const unsigned blocks = (unsigned)((T * F + 255) / 256);
+    if (dt == GGB_TYPE_BF16) act_rows_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(x, ldx, T, F, act, (__nv_bfloat16 *)y);
+    else act_rows_kernel<<<blocks, 256, 0, ggb_cuda_stream()>>>(x, ldx, T, F, act, (float *)y);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+} // extern "C"

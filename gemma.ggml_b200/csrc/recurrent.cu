@@ -96,7 +96,7 @@ constexpr int kChunk = 16;  // tokens staged at once
 
 struct rec_args {
     const float *q, *k, *v, *b, *a;
-    int64_t ld, ld_ba, T;
+    int64_t ld, ld_b, ld_a, T;
     int H, G, D, Dv;
     const float *decay, *A_log, *dt_bias;
     float *state, *o;
@@ -105,25 +105,29 @@ struct rec_args {
 
 // MODE 0: lightning (q, k, v = silu of the raw rows; S <- decay S + k v^T; o = S^T q)
 // MODE 1: gated delta rule (unit q and k, q * D^-1/2; S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q)
+// MODE 2: the same rule with one decay per head and key channel: row d of S is multiplied by g[d]; the decays of a
+//         token are staged like a q / k row
 //
 // CV * 4 threads run the recurrence on the chunk in one buffer while four more warps stage the next chunk into
 // the other (global loads of a warp's four tokens in flight together), one barrier per chunk.
 // A lane's slice of a q / k row starts DS + 4 words after its neighbour's: the four 16-byte reads of a warp fall into
 // four different groups of banks (DS alone is a multiple of 8 words: all four would meet in one).
-template <int DS, int CV>
+template <int DS, int CV, bool CH = false>
 struct rec_smem {
     static constexpr int DP = DS * kNS;        // padded D
     static constexpr int DW = (DS + 4) * kNS;  // words of a staged row
     __device__ static __forceinline__ int at(int d) { return (d / DS) * (DS + 4) + d % DS; }
     float q[kChunk][DW], k[kChunk][DW];
     float v[kChunk][CV], g[kChunk], beta[kChunk];
+    float gc[kChunk][CH ? DW : 1]; // per-channel decays
 };
 
 template <int DS, int CV, int MODE>
-__device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV> &b, int64_t t0, int n, int h, int hk, int col0, int pw, int lane, float a_rate,
+__device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV, MODE == 2> &b, int64_t t0, int n, int h, int hk, int col0, int pw, int lane, float a_rate,
                                           float dtb, float q_scale) {
     constexpr int DP = DS * kNS, PL = (DP + 31) / 32, TPW = kChunk / kStageWarps; // numbers per lane and row, tokens per producer warp
     float qv[TPW][PL], kv[TPW][PL], vv[TPW], bb[TPW], aa[TPW];
+    float av[MODE == 2 ? TPW : 1][MODE == 2 ? PL : 1];
 #pragma unroll
     for (int u = 0; u < TPW; u++) {
         const int tt = pw + kStageWarps * u;
@@ -137,8 +141,17 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV> &b
         }
         vv[u] = (lane < CV && col0 + lane < p.Dv) ? p.v[t * p.ld + (int64_t)h * p.Dv + col0 + lane] : 0.f;
         if (MODE == 1) {
-            bb[u] = p.b[t * p.ld_ba + h];
-            aa[u] = p.a[t * p.ld_ba + h];
+            bb[u] = p.b[t * p.ld_b + h];
+            aa[u] = p.a[t * p.ld_a + h];
+        }
+        if (MODE == 2) {
+            bb[u] = p.b[t * p.ld_b + h];
+            const float *ar = p.a + t * p.ld_a + (int64_t)h * p.D;
+#pragma unroll
+            for (int i = 0; i < PL; i++) {
+                const int d = lane + 32 * i;
+                av[u][i] = d < p.D ? ar[d] : 0.f;
+            }
         }
     }
 #pragma unroll
@@ -166,15 +179,23 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV> &b
             km = 1.0f / sqrtf(ks + 1e-6f);
             if (lane == 0) {
                 b.beta[tt] = sigmoid_f32(bb[u]);
-                b.g[tt] = expf(-a_rate * softplus_f32(aa[u] + dtb));
+                if (MODE == 1) b.g[tt] = expf(-a_rate * softplus_f32(aa[u] + dtb));
+            }
+            if (MODE == 2) {
+#pragma unroll
+                for (int i = 0; i < PL; i++) {
+                    const int d = lane + 32 * i;
+                    if (d < DP) // rows of the padding hold zeros and stay zero
+                        b.gc[tt][rec_smem<DS, CV, true>::at(d)] = d < p.D ? expf(-a_rate * softplus_f32(av[u][i] + p.dt_bias[(int64_t)h * p.D + d])) : 1.f;
+                }
             }
         }
 #pragma unroll
         for (int i = 0; i < PL; i++) {
             const int d = lane + 32 * i;
             if (d < DP) {
-                b.q[tt][rec_smem<DS, CV>::at(d)] = qv[u][i] * qm;
-                b.k[tt][rec_smem<DS, CV>::at(d)] = kv[u][i] * km;
+                b.q[tt][rec_smem<DS, CV, MODE == 2>::at(d)] = qv[u][i] * qm;
+                b.k[tt][rec_smem<DS, CV, MODE == 2>::at(d)] = kv[u][i] * km;
             }
         }
         if (lane < CV) b.v[tt][lane] = vv[u];
@@ -184,13 +205,14 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV> &b
 template <int DS, int CV, int MODE>
 __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(rec_args p) {
     extern __shared__ __align__(16) unsigned char rec_raw[];
-    rec_smem<DS, CV> *buf = reinterpret_cast<rec_smem<DS, CV> *>(rec_raw);
+    typedef rec_smem<DS, CV, MODE == 2> smem_t;
+    smem_t *buf = reinterpret_cast<smem_t *>(rec_raw);
     const int h = blockIdx.x, col0 = blockIdx.y * CV;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool producer = warp >= (CV * kNS) / 32;
     const int s = tid % kNS, cl = (tid / kNS) % CV, col = col0 + cl;
     const bool live = !producer && col < p.Dv;
-    const int hk = MODE == 1 ? h / (p.H / p.G) : h; // the q / k head this head reads
+    const int hk = MODE != 0 ? h / (p.H / p.G) : h; // the q / k head this head reads
     float S[DS];
     float *sp = p.state + ((int64_t)h * p.D) * p.Dv + col;
 #pragma unroll
@@ -199,7 +221,7 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
         S[i] = (live && d < p.D) ? sp[(int64_t)d * p.Dv] : 0.f;
     }
     const float decay = MODE == 0 ? p.decay[h] : 0.f;
-    const float a_rate = MODE == 1 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
+    const float a_rate = MODE != 0 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
     const float q_scale = 1.0f / sqrtf((float)p.D);
     const int pw = warp - (CV * kNS) / 32;
     if (producer) rec_stage<DS, CV, MODE>(p, buf[0], 0, (int)min((int64_t)kChunk, p.T), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
@@ -211,7 +233,7 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
             if (t0 + kChunk < p.T)
                 rec_stage<DS, CV, MODE>(p, buf[cur ^ 1], t0 + kChunk, (int)min((int64_t)kChunk, p.T - t0 - kChunk), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
         } else {
-            const rec_smem<DS, CV> &b = buf[cur];
+            const smem_t &b = buf[cur];
             for (int tt = 0; tt < n; tt++) {
                 const float4 *k4 = reinterpret_cast<const float4 *>(&b.k[tt][s * (DS + 4)]);
                 const float4 *q4 = reinterpret_cast<const float4 *>(&b.q[tt][s * (DS + 4)]);
@@ -231,15 +253,17 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
                         o1 = fmaf(S[4 * i + 3], qq.w, o1);
                     }
                 } else {
-                    const float g = b.g[tt];
+                    const float g = MODE == 1 ? b.g[tt] : 1.f;
+                    const float4 *g4 = reinterpret_cast<const float4 *>(&b.gc[MODE == 2 ? tt : 0][MODE == 2 ? s * (DS + 4) : 0]);
                     float r0 = 0.f, r1 = 0.f;
 #pragma unroll
                     for (int i = 0; i < DS / 4; i++) {
                         const float4 kk = k4[i];
-                        S[4 * i + 0] *= g;
-                        S[4 * i + 1] *= g;
-                        S[4 * i + 2] *= g;
-                        S[4 * i + 3] *= g;
+                        const float4 gg = MODE == 2 ? g4[i] : make_float4(g, g, g, g);
+                        S[4 * i + 0] *= gg.x;
+                        S[4 * i + 1] *= gg.y;
+                        S[4 * i + 2] *= gg.z;
+                        S[4 * i + 3] *= gg.w;
                         r0 = fmaf(S[4 * i + 0], kk.x, r0);
                         r1 = fmaf(S[4 * i + 1], kk.y, r1);
                         r0 = fmaf(S[4 * i + 2], kk.z, r0);
@@ -280,7 +304,7 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
 template <int DS, int CV, int MODE>
 int recurrence_launch_cv(const rec_args &p) {
     const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + CV - 1) / CV));
-    const size_t smem = 2 * sizeof(rec_smem<DS, CV>);
+    const size_t smem = 2 * sizeof(rec_smem<DS, CV, MODE == 2>);
     auto k = recurrence_kernel<DS, CV, MODE>;
     if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<grid, CV * kNS + 32 * kStageWarps, smem, ggb_cuda_stream()>>>(p);
@@ -335,7 +359,7 @@ int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_
     GGB_REQUIRE_INIT();
     GGB_CHECK_ARG(q && k && v && decay && state && o && T > 0 && H > 0 && D > 0 && D <= 64 * kNS && Dv > 0 && ldo >= (int64_t)H * Dv,
                   "lightning_attn: bad arguments (key size %d, at most %d)", D, 64 * kNS);
-    rec_args p{q, k, v, nullptr, nullptr, ld, 0, T, H, H, D, Dv, decay, nullptr, nullptr, state, o, ldo};
+    rec_args p{q, k, v, nullptr, nullptr, ld, 0, 0, T, H, H, D, Dv, decay, nullptr, nullptr, state, o, ldo};
     return recurrence_launch<0>(p);
 }
 
@@ -345,8 +369,18 @@ int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t l
     GGB_CHECK_ARG(q && k && v && b && a && A_log && dt_bias && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 64 * kNS &&
                       Dv > 0 && ldo >= (int64_t)H * Dv,
                   "gated_delta: bad arguments (heads %d over %d key heads, key size %d)", H, G, D);
-    rec_args p{q, k, v, b, a, ld, ld_ba, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
+    rec_args p{q, k, v, b, a, ld, ld_ba, ld_ba, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
     return recurrence_launch<1>(p);
+}
+
+int ggb_op_channel_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, int64_t ld_b, const float *a, int64_t ld_a,
+                         int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(q && k && v && b && a && A_log && dt_bias && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 64 * kNS &&
+                      Dv > 0 && ldo >= (int64_t)H * Dv && ld_a >= (int64_t)H * D && ld_b >= H,
+                  "channel_delta: bad arguments (heads %d over %d key heads, key size %d)", H, G, D);
+    rec_args p{q, k, v, b, a, ld, ld_b, ld_a, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
+    return recurrence_launch<2>(p);
 }
 
 } // extern "C"

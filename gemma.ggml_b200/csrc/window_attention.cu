@@ -14,6 +14,11 @@
 //   steps of few tokens (window_attn_kernel): 8 warps split one (token, head)'s keys, rows straight from the cache
 //   (several loads in flight), parts merged through shared memory.
 //
+// The same kernels serve other masks and layouts, all arguments: the visible range of a query is a sliding window or the
+// chunk of consecutive positions it lies in (chunks counted from position 0), a score may pass a soft cap
+// cap * tanh(s / cap) before the soft-max, and the rotary pairs of q and k are neighbours (2i, 2i + 1) or halves
+// (i, i + rot_dims / 2).
+//
 // Compiled with -fmad=false: multiply-adds are spelled fmaf().
 #include <algorithm>
 
@@ -26,10 +31,17 @@ constexpr int kMaxDvRegs = 8; // value coordinates per lane: Dv <= 32 * kMaxDvRe
 constexpr int kWarps = 8;
 constexpr int kMaxSplit = 16; // CTAs that share one (token, head) of a short step
 
+// the first position the query at position i sees: everything (size <= 0), the last `size` positions, or its chunk
+__device__ __forceinline__ int64_t first_visible(int64_t i, int64_t size, int chunked) {
+    if (size <= 0) return 0;
+    return chunked ? i - i % size : max((int64_t)0, i - size + 1);
+}
+__device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+
 template <typename E>
 __global__ void __launch_bounds__(256) window_qkv_store_kernel(const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                                int64_t ld, int H, int G, int D, int Dv, const float *__restrict__ qn_w,
-                                                               const float *__restrict__ kn_w, float eps, int rot_dims,
+                                                               const float *__restrict__ kn_w, float eps, int rot_dims, int rot_halves,
                                                                const float *__restrict__ cs_k, const float *__restrict__ cs_v, float scale,
                                                                const int32_t *__restrict__ pos0, const int32_t *__restrict__ table, int B,
                                                                E *__restrict__ cache, int64_t cache_ld, float *__restrict__ q_out) {
@@ -61,31 +73,38 @@ __global__ void __launch_bounds__(256) window_qkv_store_kernel(const float *__re
     }
     E *row = cache + ((int64_t)table[pos / B] * B + pos % B) * cache_ld;
     const float *ck = cs_k ? cs_k + pos * (rot_dims / 2) * 2 : nullptr;
-    // pairs (2i, 2i + 1) of q and k
+    // pairs of q and k: pair m of a head is (2m, 2m + 1), or with rot_halves (m, m + rot_dims / 2) for the rotated pairs and
+    // the neighbours behind them for the rest; pair m < rot_dims / 2 turns by the table's entry m
     for (int p = threadIdx.x; p < (nq + nk) / 2; p += blockDim.x) {
         const bool is_q = p < nq / 2;
         const int e = is_q ? 2 * p : 2 * p - nq; // even coordinate inside the projection
         const float *src = is_q ? qr : kr;
         const float *nw = is_q ? qn_w : kn_w;
         const float r = is_q ? rq : rk;
-        float u = src[e], w = src[e + 1];
-        if (nw) {
-            u = u * r * nw[e];
-            w = w * r * nw[e + 1];
+        const int d = e % D, m = d / 2;
+        const bool turn = ck && d < rot_dims;
+        int e0 = e, e1 = e + 1;
+        if (rot_halves) {
+            if (turn) e0 = e - d + m, e1 = e0 + rot_dims / 2;
+            else e0 = e - d + rot_dims + 2 * (m - rot_dims / 2), e1 = e0 + 1;
         }
-        const int d = e % D;
-        if (ck && d < rot_dims) {
-            const float c = ck[d], s = ck[d + 1]; // pair d / 2: [cos, sin]
+        float u = src[e0], w = src[e1];
+        if (nw) {
+            u = u * r * nw[e0];
+            w = w * r * nw[e1];
+        }
+        if (turn) {
+            const float c = ck[d], s = ck[d + 1]; // pair m: [cos, sin]
             const float u2 = u * c - w * s, w2 = w * c + u * s;
             u = u2;
             w = w2;
         }
         if (is_q) {
-            q_out[t * nq + e] = u * scale;
-            q_out[t * nq + e + 1] = w * scale;
+            q_out[t * nq + e0] = u * scale;
+            q_out[t * nq + e1] = w * scale;
         } else {
-            row[e] = from_f32<E>(u);
-            row[e + 1] = from_f32<E>(w);
+            row[e0] = from_f32<E>(u);
+            row[e1] = from_f32<E>(w);
         }
     }
     const float *cv = cs_v ? cs_v + pos * (Dv / 2) * 2 : nullptr;
@@ -139,8 +158,8 @@ constexpr int kPartW = 2 + 32 * kMaxDvRegs; // one part: running maximum, sum, w
 template <typename E>
 __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                   const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
-                                                                  int64_t T, int H, int G, int D, int Dv, int64_t window,
-                                                                  const float *__restrict__ cs_v, E *__restrict__ out, int vec,
+                                                                  int64_t T, int H, int G, int D, int Dv, int64_t window, int chunked,
+                                                                  float cap, const float *__restrict__ cs_v, E *__restrict__ out, int vec,
                                                                   float *__restrict__ part_out) {
     extern __shared__ __align__(16) float wa_smem[]; // q: [kWarps][Dp]; merge: [kWarps][kPartW]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -153,7 +172,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
         for (int d = lane; d < Dp; d += 32) sq[d] = d < D ? q[(t * H + h) * D + d] : 0.f;
     __syncwarp();
     const int64_t i = (int64_t)*pos0 + (active ? t : 0);
-    const int64_t jlo = window > 0 ? max((int64_t)0, i - window + 1) : 0;
+    const int64_t jlo = first_visible(i, window, chunked);
     const int nreg = (Dv + 63) / 64; // pairs of coordinates per lane: c = 2 * lane + 64 * r
     float acc[kMaxDvRegs];
 #pragma unroll
@@ -186,7 +205,7 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_kernel(const float *_
                 } else {
                     for (int d = 0; d < D; d++) a0 = fmaf(to_f32(kr[d]), sq[d], a0);
                 }
-                s = a0 + a1;
+                s = soft_cap(a0 + a1, cap);
             }
             const float m_new = fmaxf(m, warp_max_f32(s)); // finite: key j0 of the tile is always visible
             const float p = j <= i ? expf(s - m_new) : 0.f;
@@ -300,7 +319,7 @@ template <typename E, int NP, bool VEC>
 __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const float *__restrict__ q, const E *__restrict__ cache, int64_t cache_ld,
                                                                        const int32_t *__restrict__ table, int B, const int32_t *__restrict__ pos0,
                                                                        int64_t T, int H, int G, int D, int Dv, int kp, int vp, int64_t window,
-                                                                       const float *__restrict__ cs_v, E *__restrict__ out) {
+                                                                       int chunked, float cap, const float *__restrict__ cs_v, E *__restrict__ out) {
     extern __shared__ __align__(16) float wa_smem[];
     const int Dp = (D + 3) & ~3;
     float *sq = wa_smem;              // [kQT][Dp]
@@ -316,10 +335,12 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
         const int qi = e / Dp, d = e - qi * Dp;
         sq[e] = (qi < nq && d < D) ? q[((t0 + qi) * H + h) * D + d] : 0.f;
     }
-    const int64_t jlo = window > 0 ? max((int64_t)0, i0 - window + 1) : 0;
+    const int64_t jlo = first_visible(i0, window, chunked); // never later than a later query's first key
     float acc[kQPW][2 * NP], m[kQPW], l[kQPW];
+    int64_t lo[kQPW];
 #pragma unroll
     for (int a = 0; a < kQPW; a++) {
+        lo[a] = first_visible(i0 + warp * kQPW + a, window, chunked);
         m[a] = -INFINITY;
         l[a] = 0.f;
 #pragma unroll
@@ -388,8 +409,8 @@ __global__ void __launch_bounds__(32 * kWarps) window_attn_tile_kernel(const flo
         for (int a = 0; a < kQPW; a++) {
             const int64_t i = i0 + warp * kQPW + a;
             const bool live = warp * kQPW + a < nq;
-            const bool vis = live && j <= i && (window <= 0 || i - j < window);
-            const float sa = vis ? s[a] : -INFINITY;
+            const bool vis = live && j <= i && j >= lo[a];
+            const float sa = vis ? soft_cap(s[a], cap) : -INFINITY;
             const float m_new = fmaxf(m[a], warp_max_f32(sa));
             // a query none of whose keys lie in this tile keeps m = -inf: nothing to rescale, nothing to add
             const float corr = m_new == -INFINITY ? 1.f : expf(m[a] - m_new);
@@ -435,6 +456,14 @@ int64_t ggb_window_cache_ld(int G, int D, int Dv) { return (((int64_t)G * (D + D
 int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
                             const float *qn_w, const float *kn_w, float eps, int rot_dims, const float *cos_sin_k, const float *cos_sin_v,
                             float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache, float *q_out) {
+    return ggb_op_masked_qkv_store(dt, q, k, v, ld, T, H, G, D, Dv, qn_w, kn_w, eps, rot_dims, 0, cos_sin_k, cos_sin_v, scale, pos0, block_table,
+                                   block_size, cache, q_out);
+}
+
+int ggb_op_masked_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
+                            const float *qn_w, const float *kn_w, float eps, int rot_dims, int rot_halves, const float *cos_sin_k,
+                            const float *cos_sin_v, float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache,
+                            float *q_out) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "window_qkv_store: dtype %d is neither bf16 nor f32", dt);
     GGB_CHECK_ARG(q && k && v && pos0 && block_table && cache && q_out && T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0,
@@ -443,11 +472,11 @@ int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float 
                   "window_qkv_store: head sizes %d / %d and %d rotated dimensions must be even", D, Dv, rot_dims);
     const int64_t cld = ggb_window_cache_ld(G, D, Dv);
     if (dt == GGB_TYPE_BF16)
-        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims,
+        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims, rot_halves,
                                                                             rot_dims ? cos_sin_k : nullptr, cos_sin_v, scale, pos0, block_table,
                                                                             block_size, (__nv_bfloat16 *)cache, cld, q_out);
     else
-        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims,
+        window_qkv_store_kernel<<<(unsigned)T, 256, 0, ggb_cuda_stream()>>>(q, k, v, ld, H, G, D, Dv, qn_w, kn_w, eps, rot_dims, rot_halves,
                                                                             rot_dims ? cos_sin_k : nullptr, cos_sin_v, scale, pos0, block_table,
                                                                             block_size, (float *)cache, cld, q_out);
     GGB_LAUNCH_CHECK();
@@ -458,7 +487,14 @@ size_t ggb_window_attn_scratch_bytes(int H) { return (size_t)(kQT - 1) * (size_t
 
 int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
                        int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out, float *scratch) {
+    return ggb_op_masked_attn(dt, q, cache, block_table, block_size, pos0, T, H, G, D, Dv, window, 0, 0.f, cos_sin_v, out, scratch);
+}
+
+int ggb_op_masked_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
+                       int H, int G, int D, int Dv, int64_t window, int chunked, float softcap, const float *cos_sin_v, void *out,
+                       float *scratch) {
     GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(softcap >= 0.f && (chunked == 0 || chunked == 1), "masked_attn: the soft cap must not be negative");
     GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "window_attn: dtype %d is neither bf16 nor f32", dt);
     GGB_CHECK_ARG(q && cache && block_table && pos0 && out && T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && D > 0 && Dv > 0 &&
                       Dv % 2 == 0 && Dv <= 32 * kMaxDvRegs,
@@ -485,7 +521,7 @@ int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t 
         auto kfn = window_attn_tile_kernel<ET, NP, VEC>;                                                                     \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));    \
         kfn<<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, kp, vp, \
-                                             window, cos_sin_v, (ET *)out);                                                  \
+                                             window, chunked, softcap, cos_sin_v, (ET *)out);                                                  \
     }
 #define WT_NP(ET, VEC)                             \
     {                                              \
@@ -511,7 +547,7 @@ int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t 
         const dim3 grid((unsigned)T, (unsigned)H, (unsigned)n_split);
 #define WS_LAUNCH(ET)                                                                                                                        \
     window_attn_kernel<ET><<<grid, 32 * kWarps, smem, st>>>(q, (const ET *)cache, cld, block_table, block_size, pos0, T, H, G, D, Dv, window,  \
-                                                            cos_sin_v, (ET *)out, vec, scratch);                                             \
+                                                            chunked, softcap, cos_sin_v, (ET *)out, vec, scratch);                                             \
     if (n_split > 1) {                                                                                                                       \
         GGB_LAUNCH_CHECK();                                                                                                                  \
         window_merge_kernel<ET><<<dim3((unsigned)T, (unsigned)H), 32, 0, st>>>(scratch, n_split, pos0, H, Dv, cos_sin_v, (ET *)out);          \

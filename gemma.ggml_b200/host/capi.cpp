@@ -11,6 +11,7 @@
 #include "lm_engine.h"
 #include "begupel_model.h"
 #include "ditalorn_model.h"
+#include "kibilix_model.h"
 #include "safolorn_model.h"
 #include "tensor_dump.h"
 
@@ -238,6 +239,23 @@ int dl_config_probe(const char *text, int64_t *out) {
     }
     out[0] = (int64_t)c.layers.size(); out[1] = attn; out[2] = lat; out[3] = moe; out[4] = c.vocab; out[5] = c.width;
     out[6] = c.max_positions; out[7] = bounded ? win : 0;
+    return 0;
+}
+// host only: parses a Kibilix configuration text; out[8] = {layers, layer runs, attention runs, channel_delta runs, layers with
+// experts, vocab, width, streams}; -1 and gm_last_error() when it is refused
+int kb_config_probe(const char *text, int64_t *out) {
+    json_value j;
+    kb_config c;
+    if (!json_parser(text, strlen(text)).parse(&j, &g_capi_err)) return -1;
+    if (kb_parse_config(j, nullptr, &c, &g_capi_err)) return -1;
+    int64_t attn = 0, delta = 0, moe = 0;
+    for (int li : c.runs) {
+        attn += c.layers[(size_t)li].type == 0;
+        delta += c.layers[(size_t)li].type == 1;
+    }
+    for (const auto &l : c.layers) moe += l.ff_kind == 2;
+    out[0] = (int64_t)c.layers.size(); out[1] = (int64_t)c.runs.size(); out[2] = attn; out[3] = delta; out[4] = moe; out[5] = c.vocab;
+    out[6] = c.width; out[7] = c.streams;
     return 0;
 }
 // host only: a tensor of a .safetensors file: returns its number of dimensions (shape[0 .. 8) filled, *nbytes, dtype text),

@@ -7,7 +7,8 @@
 
 std::string rot_spec::key() const {
     char b[256];
-    snprintf(b, sizeof b, "%d|%.17g|%d%d|%.17g|%.17g|%.17g|%.17g", dims, base, (int)scaled, (int)linear, factor, original, fast, slow);
+    snprintf(b, sizeof b, "%d|%.17g|%d%d%d|%.17g|%.17g|%.17g|%.17g|%.17g|%.17g", dims, base, (int)scaled, (int)linear, (int)banded, factor, original,
+             fast, slow, low, high);
     return b;
 }
 
@@ -27,6 +28,18 @@ std::vector<float> rot_table(const rot_spec &r, int64_t n_pos) {
         mag = 0.1 * std::log(r.factor) + 1.0;
     } else if (r.linear) {
         for (int i = 0; i < half; i++) f[(size_t)i] /= r.factor;
+    } else if (r.banded) {
+        const double two_pi = 6.283185307179586476925286766559;
+        for (int i = 0; i < half; i++) {
+            const double fi = f[(size_t)i], wave = two_pi / fi;
+            if (wave < r.original / r.high) continue;
+            if (wave > r.original / r.low) {
+                f[(size_t)i] = fi / r.factor;
+            } else {
+                const double s = (r.original / wave - r.low) / (r.high - r.low);
+                f[(size_t)i] = (1.0 - s) * fi / r.factor + s * fi;
+            }
+        }
     }
     std::vector<float> t((size_t)n_pos * (size_t)half * 2);
     for (int64_t p = 0; p < n_pos; p++)

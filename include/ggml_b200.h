@@ -299,6 +299,17 @@ int ggb_op_embed_pos(int dt, const void *table, const void *pos_table, const int
 int ggb_op_norm_add_norm(int dt, const float *a, const float *bias, const float *wa, float eps, int64_t E, int64_t T, float *x,
                          const float *wy, void *y);
 
+/* Several residual streams (hyper-connections): xs [T][S][W] fp32 holds S copies of the residual per token.  One pass:
+ * with x0 ([T][W]) every stream starts as that row; with y ([T][W], a sublayer's output) all streams are renewed at once from
+ * the old ones, x_t <- sum_s mix[s * S + t] x_s + coef[t] y; with in_w the sum u = sum_s in_w[s] x_s is read out as fp32
+ * (u_out, may be NULL) and / or normed in dt (h = u / sqrt(mean(u^2) + eps) * nw, may be NULL).  rows (device int32, may be
+ * NULL): only the tokens rows[0 .. T) are read out (outputs dense in that order) and xs is left as it was: what y brings
+ * enters on the way.  One stream with mix = in_w = {1} is the plain residual sum. */
+int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const float *mix, const float *coef, int S, const float *in_w,
+                     const float *nw, float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h);
+/* y (dt, dense [T][F]) = act(x), x fp32 rows of stride ldx; act 0: as it is, 1: relu(x)^2 */
+int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y);
+
 /* ------------------------------------------------------------------ recurrent mixers (csrc/recurrent.cu)
  * State that a sequence carries from token to token (fp32, one block per sequence, handed in by the caller): tails of
  * causal convolutions and the matrices S [heads][D][Dv] of linear-attention recurrences.
@@ -323,6 +334,12 @@ int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_
 int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, const float *a, int64_t ld_ba, int64_t T,
                        int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo);
 
+/* the gated delta rule with one decay per head and key channel: a [T][H * D] raw rows (row stride ld_a), dt_bias [H * D],
+ * b [T][H] (row stride ld_b); g[h][d] = exp(-exp(A_log[h]) softplus(a[h][d] + dt_bias[h][d])) multiplies row d of the head's
+ * S [D][Dv] before the token's write; everything else as ggb_op_gated_delta */
+int ggb_op_channel_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, int64_t ld_b, const float *a, int64_t ld_a,
+                         int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo);
+
 /* ------------------------------------------------------------------ sliding-window attention (csrc/window_attention.cu)
  * Grouped-query soft-max attention over a paged cache whose row per position is [k (G * D) | v (G * Dv)] in dt,
  * ggb_window_cache_ld numbers apart (pages as in the latent cache).  Values are stored rotated by their own position
@@ -343,6 +360,18 @@ int ggb_op_window_qkv_store(int dt, const float *q, const float *k, const float 
 size_t ggb_window_attn_scratch_bytes(int H);
 int ggb_op_window_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
                        int H, int G, int D, int Dv, int64_t window, const float *cos_sin_v, void *out, float *scratch);
+
+/* The same two operators with every choice an argument.  rot_halves 1: the rotated pair m < rot_dims / 2 of a head is
+ * (m, m + rot_dims / 2) instead of (2m, 2m + 1) (the table's entry m turns it either way).  chunked 1: `window` is a chunk
+ * size and the query at position i sees the keys j <= i with floor(j / window) == floor(i / window), chunks counted from
+ * position 0 of the sequence.  softcap > 0: a score s enters the soft-max as softcap * tanh(s / softcap). */
+int ggb_op_masked_qkv_store(int dt, const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int G, int D, int Dv,
+                            const float *qn_w, const float *kn_w, float eps, int rot_dims, int rot_halves, const float *cos_sin_k,
+                            const float *cos_sin_v, float scale, const int32_t *pos0, const int32_t *block_table, int block_size, void *cache,
+                            float *q_out);
+int ggb_op_masked_attn(int dt, const float *q, const void *cache, const int32_t *block_table, int block_size, const int32_t *pos0, int64_t T,
+                       int H, int G, int D, int Dv, int64_t window, int chunked, float softcap, const float *cos_sin_v, void *out,
+                       float *scratch);
 
 /* ------------------------------------------------------------------ sigmoid attention (csrc/sigmoid_attention.cu)
  * Grouped-query attention with unnormalised weights over the same paged rows [k (G * D) | v (G * Dv)] (ggb_window_cache_ld):
@@ -429,6 +458,22 @@ int ggb_op_moe_combine(const float *y, const int32_t *ws, const float *wt, int64
 #define GGB_MOE_COMBINE_NORM_MAX_TOP 64 /* more slots per token: ggb_op_moe_combine, then ggb_op_norm_add_norm */
 int ggb_op_moe_combine_norm(int dt, const float *y, const int32_t *ws, const float *wt, int64_t T, int top, int n_exp, int64_t W, const float *wa,
                             float eps, float *x, const float *wy, void *out);
+
+/* route with soft-max scores over ALL experts: s = softmax(w_router h) in fp32; the `top` largest s + correction (may be
+ * NULL) win (ties: the lower index); the weights are the chosen experts' s divided by their sum (+ 1e-20).  ws as for
+ * ggb_op_moe_route_sigmoid. */
+int ggb_op_moe_route_softmax(int dt, const void *h, int64_t W, int64_t T, const float *w_router, const float *correction, int n_exp, int top,
+                             float *logits /* scratch [T][n_exp] */, int32_t *idx, float *wt, int32_t *ws);
+/* Identity experts: the last n_identity of the n_exp experts have no matrices and hand their input through.  Their slots
+ * are grouped like the others but no product touches them (w holds n_exp - n_identity experts), and the weighted sum takes
+ * the token's row of h (dt, [T][W]: what the experts read) in their place.  moe_linear act 3 (steps of at most 16 slots):
+ * w = [experts][2 N][K] (N gate rows, then N up rows), c (dt) = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit),
+ * u = clamp(up, -limit, limit). */
+int ggb_op_moe_group_identity(const int32_t *idx, int64_t T, int top, int n_exp, int n_identity, int32_t *ws);
+int ggb_op_moe_linear_identity(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int gather, int64_t T, int top, int n_exp,
+                               int n_identity, const int32_t *ws, int act, float limit, float alpha, void *c, int64_t ldc);
+int ggb_op_moe_combine_identity(int dt, const float *y, const int32_t *ws, const float *wt, const int32_t *idx, int64_t T, int top, int n_exp,
+                                int n_identity, int64_t W, const void *h, float *out);
 
 /* ------------------------------------------------------------------ fused decode step
  * The whole per-token node list (ref: src/gemma_model.cpp:665-747) as ONE persistent cooperative
