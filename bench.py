@@ -742,7 +742,7 @@ BEGUPEL_SIZES = {  # width, layers, heads, kv heads, head size, window, delta he
 
 def begupel_config(size):
     """Layers alternate: window attention beside a gated delta rule, then lightning attention; each with a dense feed-forward."""
-    W, L, H, G, D, win, Hr, Gr, Hl, ff, V = BEGUPEL_SIZES[size]
+    W, L, H, G, D, win, Hr, Gr, Hl, ff, V = BEGUPEL_SIZES[size] if isinstance(size, str) else size
     layers = []
     for i in range(L):
         if i % 2 == 0:
@@ -800,6 +800,47 @@ def _engine_times(G, eng, V, T, ctx, n_dec, ops):
     return pf, pf_ops, dec, dc_ops, kernels, clocks.summary()
 
 
+def _begupel_record(G, peaks, dims, T, ctx, n_dec):
+    """prefill and decode of the Begupel design at the sizes `dims` (a row of BEGUPEL_SIZES) with its roofline fractions"""
+    cfg = begupel_config(dims)
+    W, nl, H, Gk, D, win, Hr, Gr, Hl, ff, V = dims
+    eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+    pf, pf_ops, dec, dc_ops, kernels, clocks = _engine_times(G, eng, V, T, ctx, n_dec, BG_OPS)
+    wbytes = eng.stats()["weight_bytes"]
+    eng.close()
+    lin_params = attn_flops = rec_flops = 0.0
+    cache_bytes = state_bytes = 0.0
+    visible = float(sum(min(i + 1, win) for i in range(T)))
+    for Ly in cfg["layers"]:
+        if Ly["type"] == "parallel":
+            lin_params += W * (H * D + 2 * Gk * D) + W * H * D + W * (2 * Gr * D + 2 * Hr * D + 2 * Hr) + W * Hr * D
+            attn_flops += 4.0 * H * D * visible
+            rec_flops += 7.0 * Hr * D * D * T
+            cache_bytes += 2.0 * min(ctx, win) * 2 * Gk * D
+            state_bytes += 8.0 * Hr * D * D
+        else:
+            lin_params += W * 4 * Hl * D + W * Hl * D
+            rec_flops += 4.0 * Hl * D * D * T
+            state_bytes += 8.0 * Hl * D * D
+        lin_params += 3.0 * ff * W
+    lin_flops = 2.0 * T * lin_params + 2.0 * V * W
+    lin_bytes = 2.0 * (lin_params + V * W)
+    rec = {
+        "config": {"width": W, "layers": nl, "heads": H, "kv_heads": Gk, "dim": D, "window": win, "delta_heads": Hr, "delta_kv_heads": Gr,
+                   "lightning_heads": Hl, "ff": ff, "vocab": V, "weight_bytes": wbytes},
+        "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks,
+                    "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
+                    "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                    "attn_tflops_cuda_cores": attn_flops / (pf_ops["op_attn"] / 1e3) / 1e12,
+                    "recurrence_tflops_cuda_cores": rec_flops / (pf_ops["op_recurrence"] / 1e3) / 1e12},
+        "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
+                   "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                   "attn_gbs": cache_bytes / (dc_ops["op_attn"] / 1e3) / 1e9, "recurrence_gbs": state_bytes / (dc_ops["op_recurrence"] / 1e3) / 1e9,
+                   "token_frac_of_hbm_roofline": ((lin_bytes + cache_bytes + state_bytes) / (peaks["hbm_gbs"] * 1e9)) / dec},
+    }
+    return rec
+
+
 def run_begupel(args):
     """--arch begupel: prefill and decode throughput of the Begupel design (random bf16 weights) at layer sizes of real
     models, through the serving engine (host call: H2D token ids, operator launches / graph replay, D2H result), with
@@ -816,42 +857,8 @@ def run_begupel(args):
     T, ctx, n_dec = args.prefill_tokens if args.prefill_tokens != 512 else 2048, args.ctx, min(args.steps, 128)
     records = {}
     for size in args.sizes.split(","):
-        cfg = begupel_config(size)
         W, nl, H, Gk, D, win, Hr, Gr, Hl, ff, V = BEGUPEL_SIZES[size]
-        eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
-        pf, pf_ops, dec, dc_ops, kernels, clocks = _engine_times(G, eng, V, T, ctx, n_dec, BG_OPS)
-        wbytes = eng.stats()["weight_bytes"]
-        eng.close()
-        lin_params = attn_flops = rec_flops = 0.0
-        cache_bytes = state_bytes = 0.0
-        visible = float(sum(min(i + 1, win) for i in range(T)))
-        for Ly in cfg["layers"]:
-            if Ly["type"] == "parallel":
-                lin_params += W * (H * D + 2 * Gk * D) + W * H * D + W * (2 * Gr * D + 2 * Hr * D + 2 * Hr) + W * Hr * D
-                attn_flops += 4.0 * H * D * visible
-                rec_flops += 7.0 * Hr * D * D * T
-                cache_bytes += 2.0 * min(ctx, win) * 2 * Gk * D
-                state_bytes += 8.0 * Hr * D * D
-            else:
-                lin_params += W * 4 * Hl * D + W * Hl * D
-                rec_flops += 4.0 * Hl * D * D * T
-                state_bytes += 8.0 * Hl * D * D
-            lin_params += 3.0 * ff * W
-        lin_flops = 2.0 * T * lin_params + 2.0 * V * W
-        lin_bytes = 2.0 * (lin_params + V * W)
-        rec = {
-            "config": {"width": W, "layers": nl, "heads": H, "kv_heads": Gk, "dim": D, "window": win, "delta_heads": Hr, "delta_kv_heads": Gr,
-                       "lightning_heads": Hl, "ff": ff, "vocab": V, "weight_bytes": wbytes},
-            "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks,
-                        "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
-                        "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
-                        "attn_tflops_cuda_cores": attn_flops / (pf_ops["op_attn"] / 1e3) / 1e12,
-                        "recurrence_tflops_cuda_cores": rec_flops / (pf_ops["op_recurrence"] / 1e3) / 1e12},
-            "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
-                       "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
-                       "attn_gbs": cache_bytes / (dc_ops["op_attn"] / 1e3) / 1e9, "recurrence_gbs": state_bytes / (dc_ops["op_recurrence"] / 1e3) / 1e9,
-                       "token_frac_of_hbm_roofline": ((lin_bytes + cache_bytes + state_bytes) / (peaks["hbm_gbs"] * 1e9)) / dec},
-        }
+        rec = _begupel_record(G, peaks, BEGUPEL_SIZES[size], T, ctx, n_dec)
         if not args.no_sub_records:  # Safolorn at equal size: latent attention with heads of the same size, dense feed-forward everywhere
             R = 512 if W >= 2048 else 256
             mx = {"heads": H, "dim": D, "rot_dim": 64, "vdim": D, "kv_rank": R, "scale": (D + 64) ** -0.5,
@@ -996,12 +1003,112 @@ def run_ditalorn(args):
                       "peaks": peaks, "sizes": records}), flush=True)
 
 
+KIBILIX_SIZES = {  # width, layers, heads, kv heads, head size, chunk, delta heads, delta kv heads, dense ff, experts, identity, top, expert ff, vocab
+    "s": (1024, 8, 8, 2, 128, 1024, 8, 4, 4096, 16, 2, 2, 1024, 32000),
+    "m": (2048, 8, 16, 4, 128, 1024, 16, 8, 8192, 32, 2, 4, 1408, 32000),
+    "l": (4096, 4, 32, 8, 128, 2048, 32, 16, 12288, 16, 2, 2, 2048, 32000),
+}
+KB_OPS = ("op_linear", "op_attn", "op_attn_prep", "op_recurrence", "op_conv", "op_norm", "op_act", "op_residual", "op_rows", "op_moe", "op_moe_linear")
+KB_RANK, KB_STREAMS = 64, 4
+
+
+def kibilix_config(size):
+    """Layers alternate: a delta rule with per-channel decay, then chunked attention; the feed-forward is dense in the first
+    layer of every four and a mixture of experts with identity experts in the third; four residual streams."""
+    W, L, H, G, D, chunk, Hr, Gr, ff, E, I, top, eff, V = KIBILIX_SIZES[size]
+    layers = []
+    for i in range(L):
+        if i % 2 == 0:
+            mx = {"heads": Hr, "kv_heads": Gr, "dim": D, "vdim": D, "conv": 4, "rank": KB_RANK}
+            kind = "channel_delta"
+        else:
+            mx = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 50.0, "mask": {"size": chunk},
+                  "rot": {"base": 500000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            kind = "attention"
+        mlp = {"kind": "dense", "ff": ff} if i % 4 < 2 else {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "identity": I, "top": top}}
+        layers.append({"type": kind, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Kibilix", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": KB_STREAMS,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 31}}, "layers": layers}
+
+
+def run_kibilix(args):
+    """--arch kibilix: prefill and decode throughput of the Kibilix design (random bf16 weights) at layer sizes of real
+    models, through the serving engine (host call: H2D token ids, operator launches / graph replay, D2H result), with
+    cudaEvent time per operator class and roofline fractions; beside it Begupel, the closest model of the framework
+    (the same engine, products, cache and state blocks; window attention and a delta rule with one decay per head), at the
+    same width, depth, heads and dense feed-forward size."""
+    import gemma_ggml_b200 as G
+    G.init(0)
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks = {"hbm_gbs": float(pk["hbm_gbs"]), "bf16_tflops_sustained": float(pk["bf16_tflops_sustained"]), "source": "MEASURED_PEAKS.json"}
+    except Exception:
+        pass
+    T, ctx, n_dec = args.prefill_tokens if args.prefill_tokens != 512 else 2048, args.ctx, min(args.steps, 128)
+    records = {}
+    for size in args.sizes.split(","):
+        cfg = kibilix_config(size)
+        W, nl, H, Gk, D, chunk, Hr, Gr, ff, E, I, top, eff, V = KIBILIX_SIZES[size]
+        eng = G.Engine(config=cfg, seed=7, dtype="bfloat16", max_tokens=ctx + n_dec + 64, page_size=64, max_portion=1024)
+        pf, pf_ops, dec, dc_ops, kernels, clocks = _engine_times(G, eng, V, T, ctx, n_dec, KB_OPS)
+        wbytes = eng.stats()["weight_bytes"]
+        eng.close()
+        lin_params = attn_flops = rec_flops = exp_params = 0.0
+        cache_bytes = state_bytes = stream_bytes = 0.0
+        visible = float(sum(i % chunk + 1 for i in range(T)))
+        real = top * E / float(E + I)  # slots of a token that reach an expert with matrices, if the router chose evenly
+        for Ly in cfg["layers"]:
+            if Ly["type"] == "attention":
+                lin_params += W * (H * D + 2 * Gk * D) + W * H * D
+                attn_flops += 4.0 * H * D * visible
+                cache_bytes += 2.0 * ((ctx - 1) % chunk + 1) * 2 * Gk * D
+            else:
+                lin_params += W * (2 * Gr * D + Hr * D + Hr + 2 * KB_RANK) + 2.0 * KB_RANK * Hr * D + W * Hr * D
+                rec_flops += 7.0 * Hr * D * D * T
+                state_bytes += 8.0 * Hr * D * D
+            if Ly["mlp"]["kind"] == "dense":
+                lin_params += 2.0 * ff * W
+            else:
+                exp_params += real * 3.0 * eff * W
+            stream_bytes += 2 * (2 * KB_STREAMS + 1) * W * 4.0   # two passes over the streams per layer: read, write, one output
+        lin_flops = 2.0 * T * lin_params + 2.0 * V * W
+        lin_bytes = 2.0 * (lin_params + V * W)
+        exp_flops, exp_bytes = 2.0 * T * exp_params, 2.0 * exp_params
+        rec = {
+            "config": {"width": W, "layers": nl, "heads": H, "kv_heads": Gk, "dim": D, "chunk": chunk, "delta_heads": Hr, "delta_kv_heads": Gr, "rank": KB_RANK,
+                       "streams": KB_STREAMS, "ff": ff, "experts": E, "identity": I, "top": top, "expert_ff": eff, "vocab": V, "weight_bytes": wbytes},
+            "prefill": {"tokens": T, "tokens_per_s": T / pf, "ms": 1e3 * pf, "op_ms": pf_ops, "clocks": clocks,
+                        "linear_tflops": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12,
+                        "linear_frac_of_tensor_peak": lin_flops / (pf_ops["op_linear"] / 1e3) / 1e12 / peaks["bf16_tflops_sustained"],
+                        "experts_tflops": exp_flops / (pf_ops["op_moe_linear"] / 1e3) / 1e12,
+                        "attn_tflops_cuda_cores": attn_flops / (pf_ops["op_attn"] / 1e3) / 1e12,
+                        "recurrence_tflops_cuda_cores": rec_flops / (pf_ops["op_recurrence"] / 1e3) / 1e12,
+                        "streams_gbs": T * stream_bytes / (pf_ops["op_residual"] / 1e3) / 1e9},
+            "decode": {"n_kv": ctx, "tokens_per_s": 1.0 / dec, "us_per_token": 1e6 * dec, "kernels_per_token": kernels, "op_us": {k: 1e3 * v for k, v in dc_ops.items()},
+                       "linear_gbs": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9, "linear_frac_of_hbm_peak": lin_bytes / (dc_ops["op_linear"] / 1e3) / 1e9 / peaks["hbm_gbs"],
+                       "experts_gbs": exp_bytes / (dc_ops["op_moe_linear"] / 1e3) / 1e9,
+                       "attn_gbs": cache_bytes / (dc_ops["op_attn"] / 1e3) / 1e9, "recurrence_gbs": state_bytes / (dc_ops["op_recurrence"] / 1e3) / 1e9,
+                       "token_frac_of_hbm_roofline": ((lin_bytes + exp_bytes + cache_bytes + state_bytes) / (peaks["hbm_gbs"] * 1e9)) / dec},
+        }
+        if not args.no_sub_records:  # Begupel at equal size: window = chunk, the same delta heads, as many lightning heads as attention heads
+            rec["begupel_equal_size"] = _begupel_record(G, peaks, (W, nl, H, Gk, D, chunk, Hr, Gr, H, ff, V), T, ctx, n_dec)
+        records[size] = rec
+    first = records[args.sizes.split(",")[0]]
+    print(json.dumps({"metric": "kibilix decode tokens/s", "value": first["decode"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": n_dec, "warmup": 8, "ms_per_step": first["decode"]["us_per_token"] / 1e3, "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random bf16 weights of the configured sizes)",
+                      "config": {"workload": "Kibilix sizes " + args.sizes + ": prefill of %d tokens, greedy decode at n_kv %d, through the serving engine" % (T, ctx),
+                                 "l2": "weights of every size exceed the 126 MB L2"},
+                      "peaks": peaks, "sizes": records}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn", "begupel", "ditalorn"],
+    ap.add_argument("--arch", default="gemma", choices=["gemma", "safolorn", "begupel", "ditalorn", "kibilix"],
                     help="gemma: the headline workload (default); safolorn: throughput of the Safolorn design beside Gemma at equal size; "
-                         "begupel: throughput of the Begupel design beside Safolorn at equal size; ditalorn: the Ditalorn design beside Safolorn at equal size")
-    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn / begupel / ditalorn: which of the sizes s, m, l to run")
+                         "begupel: throughput of the Begupel design beside Safolorn at equal size; ditalorn: the Ditalorn design beside Safolorn at equal size; kibilix: the Kibilix design beside Begupel at equal size")
+    ap.add_argument("--sizes", default="s,m,l", help="--arch safolorn / begupel / ditalorn / kibilix: which of the sizes s, m, l to run")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
@@ -1025,6 +1132,8 @@ def main():
         run_begupel(args)
     elif args.arch == "ditalorn":
         run_ditalorn(args)
+    elif args.arch == "kibilix":
+        run_kibilix(args)
     elif args.mode == "prefill":
         run_prefill(args)
     else:

@@ -93,11 +93,15 @@ int kb_parse_config(const json_value &j, const safetensors_file *file, kb_config
             l.type = 1;
             kb_delta_cfg &d = l.delta;
             d.heads = heads, d.kv_heads = kv_heads, d.dim = dim, d.vdim = vdim;
-            d.conv = (int)m->integer("conv", 1);
+            const std::string p = "l" + std::to_string(i) + ".mix.";
+            d.conv = (int)m->integer("conv", 0);
+            if (d.conv == 0) { // not configured: as many taps as the file's tensor has, one (of weight 1: no convolution) without it
+                const st_tensor *cw = file ? file->find(p + "q.conv") : nullptr;
+                d.conv = cw && cw->shape.size() == 2 ? (int)cw->shape[1] : 1;
+            }
             if (d.conv < 1 || d.conv > 8) return bad(where + "conv must be between 1 and 8 taps");
             if (dim > 256) return bad(where + "dim above 256 is not built");
             // the inner sizes of the two low-rank projections are the tensors' shapes; without a file, a quarter of the key size
-            const std::string p = "l" + std::to_string(i) + ".mix.";
             d.a_rank = d.g_rank = (int)m->integer("rank", std::max(8, (dim / 4 + 7) / 8 * 8));
             if (file) {
                 const st_tensor *a1 = file->find(p + "a1"), *g1 = file->find(p + "g1");
@@ -122,7 +126,7 @@ int kb_parse_config(const json_value &j, const safetensors_file *file, kb_config
                 if (!e || !r) return bad(where + "a mixture of experts needs 'expert' and 'router'");
                 kb_moe_cfg &x = l.moe;
                 x.ff = (int)e->integer("ff", 0);
-                x.limit = (float)e->number("limit", 0.0);
+                x.limit = e->get("limit") ? (float)e->number("limit", 0.0) : INFINITY; // not configured: nothing is clamped
                 x.experts = (int)r->integer("experts", 0);
                 x.identity = (int)r->integer("identity", 0);
                 x.top = (int)r->integer("top", 0);
@@ -266,12 +270,16 @@ int kibilix_model::load(const safetensors_file *file, uint64_t seed) {
             KB_TRY(push(p + "mix.g1", R.g_rank, aw, &o_g1));
             // the three convolutions side by side, as their channels lie in the stacked product
             std::vector<float> cw;
-            KB_GET(p + "mix.q.conv", G * D, R.conv, 0.5f, 0.f, &a);
-            cw.insert(cw.end(), a.begin(), a.end());
-            KB_GET(p + "mix.k.conv", G * D, R.conv, 0.5f, 0.f, &a);
-            cw.insert(cw.end(), a.begin(), a.end());
-            KB_GET(p + "mix.v.conv", H * Dv, R.conv, 0.5f, 0.f, &a);
-            cw.insert(cw.end(), a.begin(), a.end());
+            if (R.conv == 1 && file && !file->find(p + "mix.q.conv")) { // no convolution: one tap of weight 1
+                cw.assign((size_t)(2 * G * D + H * Dv), 1.0f);
+            } else {
+                KB_GET(p + "mix.q.conv", G * D, R.conv, 0.5f, 0.f, &a);
+                cw.insert(cw.end(), a.begin(), a.end());
+                KB_GET(p + "mix.k.conv", G * D, R.conv, 0.5f, 0.f, &a);
+                cw.insert(cw.end(), a.begin(), a.end());
+                KB_GET(p + "mix.v.conv", H * Dv, R.conv, 0.5f, 0.f, &a);
+                cw.insert(cw.end(), a.begin(), a.end());
+            }
             KB_TRY(upload_f32(cw, &w.conv));
             KB_F32(p + "mix.A_log", H, 1.0f, -1.0f, &w.A_log);
             KB_F32(p + "mix.dt_bias", H * D, 1.0f, 0.f, &w.dt_bias);
