@@ -172,7 +172,9 @@ _CUDA_SIG = {
     "ggb_op_sigmoid_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, vp, vp, vp, vp, vp]),
     "ggb_op_masked_qkv_store": (i32, [i32, vp, vp, vp, i64, i64, i32, i32, i32, i32, vp, vp, f32, i32, i32, vp, vp, f32, vp, vp, i32, vp, vp]),
     "ggb_op_masked_attn": (i32, [i32, vp, vp, vp, i32, vp, i64, i32, i32, i32, i32, i64, i32, f32, vp, vp, vp]),
-    "ggb_op_channel_delta": (i32, [vp, vp, vp, i64, vp, i64, vp, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, i64]),
+    "ggb_op_channel_delta": (i32, [vp, vp, vp, i64, vp, i64, vp, i64, i32, i64, i32, i32, i32, i32, vp, vp, vp, vp, i64]),
+    "ggb_lowrank_pair_fits": (i32, [i32, i32, i32]),
+    "ggb_op_lowrank_pair": (i32, [i32, vp, i64, i64, vp, i64, i32, vp, i64, i32, vp, vp, i32, vp, vp]),
     "ggb_op_moe_route_softmax": (i32, [i32, vp, i64, i64, vp, vp, i32, i32, vp, vp, vp, vp]),
     "ggb_op_moe_group_identity": (i32, [vp, i64, i32, i32, i32, vp]),
     "ggb_op_moe_linear_identity": (i32, [i32, vp, i64, i64, vp, i64, i32, i64, i32, i32, i32, vp, i32, f32, f32, vp, i64]),

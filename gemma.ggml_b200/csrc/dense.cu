@@ -784,12 +784,12 @@ constexpr int kMaxStreams = 16;
 //   in_w: u = sum_s in_w[s] x_s is read out, as fp32 (u_out) and / or normed, u / sqrt(mean(u^2) + eps) * nw, in dt (h)
 // With `rows` the CTA's token is rows[blockIdx.x] and nothing is written back to xs (a few rows read out at the end: what y
 // brings enters on the way).
-template <typename E, int SM>
+template <typename E, int SM, int V>
 __global__ void __launch_bounds__(256) hyper_mix_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y,
                                                         const float *__restrict__ mix, const float *__restrict__ coef, int S,
                                                         const float *__restrict__ in_w, const float *__restrict__ nw, float eps, int64_t W,
                                                         const int32_t *__restrict__ rows, float *__restrict__ u_out, E *__restrict__ h) {
-    extern __shared__ float hm_row[]; // [W] the read-out u
+    extern __shared__ __align__(16) float hm_row[]; // [W] the read-out u
     __shared__ float red[8], s_mix[SM * SM], s_coef[SM], s_in[SM];
     const int64_t b = blockIdx.x, t = rows ? rows[b] : b;
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[(i / S) * SM + i % S] = mix ? mix[i] : 0.f;
@@ -800,44 +800,75 @@ __global__ void __launch_bounds__(256) hyper_mix_kernel(float *xs, const float *
     __syncthreads();
     float *xr = xs + t * S * W;
     float ss = 0.f;
-    for (int64_t i = threadIdx.x; i < W; i += blockDim.x) {
-        float x[SM];
+    // V columns a thread and step (V = 4: 16-byte loads and stores, all of a column group's streams in flight together)
+    for (int64_t i = (int64_t)threadIdx.x * V; i < W; i += (int64_t)blockDim.x * V) {
+        float x[SM][V], yv[V];
 #pragma unroll
-        for (int s = 0; s < SM; s++) x[s] = s < S ? (x0 ? x0[t * W + i] : xr[s * W + i]) : 0.f;
-        if (y) {
-            const float yv = y[t * W + i];
-            float n[SM];
+        for (int s = 0; s < SM; s++) {
+            if (s < S) {
+                const float *src = x0 ? x0 + t * W + i : xr + s * W + i;
+                if (V == 4) {
+                    const float4 v4 = *reinterpret_cast<const float4 *>(src);
+                    x[s][0] = v4.x, x[s][1 % V] = v4.y, x[s][2 % V] = v4.z, x[s][3 % V] = v4.w;
+                } else {
+                    x[s][0] = src[0];
+                }
+            } else {
 #pragma unroll
-            for (int d = 0; d < SM; d++) {
-                float a = 0.f;
-#pragma unroll
-                for (int s = 0; s < SM; s++)
-                    if (s < S) a = fmaf(s_mix[s * SM + d], x[s], a);
-                n[d] = fmaf(s_coef[d], yv, a);
+                for (int c = 0; c < V; c++) x[s][c] = 0.f;
             }
+        }
+        if (y) {
+            if (V == 4) {
+                const float4 v4 = *reinterpret_cast<const float4 *>(y + t * W + i);
+                yv[0] = v4.x, yv[1 % V] = v4.y, yv[2 % V] = v4.z, yv[3 % V] = v4.w;
+            } else {
+                yv[0] = y[t * W + i];
+            }
+            float n[SM][V];
 #pragma unroll
-            for (int s = 0; s < SM; s++) x[s] = n[s];
+            for (int d = 0; d < SM; d++)
+#pragma unroll
+                for (int c = 0; c < V; c++) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int s = 0; s < SM; s++)
+                        if (s < S) a = fmaf(s_mix[s * SM + d], x[s][c], a);
+                    n[d][c] = fmaf(s_coef[d], yv[c], a);
+                }
+#pragma unroll
+            for (int s = 0; s < SM; s++)
+#pragma unroll
+                for (int c = 0; c < V; c++) x[s][c] = n[s][c];
         }
         if ((y || x0) && !rows) {
 #pragma unroll
             for (int s = 0; s < SM; s++)
-                if (s < S) xr[s * W + i] = x[s];
+                if (s < S) {
+                    if (V == 4) *reinterpret_cast<float4 *>(xr + s * W + i) = make_float4(x[s][0], x[s][1 % V], x[s][2 % V], x[s][3 % V]);
+                    else xr[s * W + i] = x[s][0];
+                }
         }
         if (in_w) {
-            float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < SM; s++)
-                if (s < S) u = fmaf(s_in[s], x[s], u);
-            if (u_out) u_out[b * W + i] = u;
-            if (h) {
-                hm_row[i] = u;
-                ss = fmaf(u, u, ss);
+            for (int c = 0; c < V; c++) {
+                float u = 0.f;
+#pragma unroll
+                for (int s = 0; s < SM; s++)
+                    if (s < S) u = fmaf(s_in[s], x[s][c], u);
+                if (u_out) u_out[b * W + i + c] = u;
+                if (h) {
+                    hm_row[i + c] = u;
+                    ss = fmaf(u, u, ss);
+                }
             }
         }
     }
     if (!h) return;
     const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)W + eps);
-    for (int64_t i = threadIdx.x; i < W; i += blockDim.x) h[b * W + i] = from_f32<E>(hm_row[i] * r * nw[i]); // a thread reads what it wrote
+    for (int64_t i = (int64_t)threadIdx.x * V; i < W; i += (int64_t)blockDim.x * V) // a thread reads what it wrote
+#pragma unroll
+        for (int c = 0; c < V; c++) h[b * W + i + c] = from_f32<E>(hm_row[i + c] * r * nw[i + c]);
 }
 
 // y (dt, dense [T][F]) = act(x) for fp32 rows of stride ldx; act 0: as it is, 1: the square of relu
@@ -863,11 +894,18 @@ int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const f
     GGB_CHECK_ARG((!y || (mix && coef)) && (!(u_out || h) || in_w) && (!h || nw), "hyper_mix: an input without its weights");
     const size_t smem = h ? (size_t)W * 4 : 0;
     GGB_CHECK_ARG(smem <= 200 * 1024, "hyper_mix: width %lld does not fit shared memory", (long long)W);
-#define HM_LAUNCH(ET, SM)                                                                                                     \
+    // 16-byte pieces need rows that start on one (up to 8 streams: the wider forms keep the registers of one column)
+    const bool vec = W % 4 == 0 && S <= 8 && (((uintptr_t)xs | (uintptr_t)x0 | (uintptr_t)y) & 15) == 0;
+#define HM_LAUNCH_V(ET, SM, V)                                                                                                \
     {                                                                                                                          \
-        auto k = hyper_mix_kernel<ET, SM>;                                                                                     \
+        auto k = hyper_mix_kernel<ET, SM, V>;                                                                                  \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
         k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h);      \
+    }
+#define HM_LAUNCH(ET, SM)                       \
+    {                                           \
+        if (vec && SM <= 8) HM_LAUNCH_V(ET, (SM <= 8 ? SM : 8), 4) \
+        else HM_LAUNCH_V(ET, SM, 1)             \
     }
 #define HM_S(ET)                              \
     {                                         \
@@ -880,6 +918,7 @@ int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const f
     if (dt == GGB_TYPE_BF16) HM_S(__nv_bfloat16) else HM_S(float)
 #undef HM_S
 #undef HM_LAUNCH
+#undef HM_LAUNCH_V
     GGB_LAUNCH_CHECK();
     return GGB_OK;
 }

@@ -10,6 +10,8 @@
 // activations, unit norms, decay and step size.
 //
 // Compiled with -fmad=false: multiply-adds are spelled fmaf().
+#include <algorithm>
+
 #include "common.cuh"
 #include "dense.cuh"
 
@@ -101,6 +103,7 @@ struct rec_args {
     const float *decay, *A_log, *dt_bias;
     float *state, *o;
     int64_t ldo;
+    int decays; // MODE 2: `a` holds the decays themselves, not the raw rows they are computed from
 };
 
 // MODE 0: lightning (q, k, v = silu of the raw rows; S <- decay S + k v^T; o = S^T q)
@@ -186,7 +189,8 @@ __device__ __forceinline__ void rec_stage(const rec_args &p, rec_smem<DS, CV, MO
                 for (int i = 0; i < PL; i++) {
                     const int d = lane + 32 * i;
                     if (d < DP) // rows of the padding hold zeros and stay zero
-                        b.gc[tt][rec_smem<DS, CV, true>::at(d)] = d < p.D ? expf(-a_rate * softplus_f32(av[u][i] + p.dt_bias[(int64_t)h * p.D + d])) : 1.f;
+                        b.gc[tt][rec_smem<DS, CV, true>::at(d)] =
+                            d >= p.D ? 1.f : p.decays ? av[u][i] : expf(-a_rate * softplus_f32(av[u][i] + p.dt_bias[(int64_t)h * p.D + d]));
                 }
             }
         }
@@ -221,7 +225,7 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
         S[i] = (live && d < p.D) ? sp[(int64_t)d * p.Dv] : 0.f;
     }
     const float decay = MODE == 0 ? p.decay[h] : 0.f;
-    const float a_rate = MODE != 0 ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
+    const float a_rate = MODE == 1 || (MODE == 2 && !p.decays) ? expf(p.A_log[h]) : 0.f, dtb = MODE == 1 ? p.dt_bias[h] : 0.f;
     const float q_scale = 1.0f / sqrtf((float)p.D);
     const int pw = warp - (CV * kNS) / 32;
     if (producer) rec_stage<DS, CV, MODE>(p, buf[0], 0, (int)min((int64_t)kChunk, p.T), h, hk, col0, pw, lane, a_rate, dtb, q_scale);
@@ -301,6 +305,73 @@ __global__ void __launch_bounds__(CV *kNS + 32 * kStageWarps) recurrence_kernel(
     }
 }
 
+// ------------------------------------------------------------------------------------------------ second halves of two low-rank projections
+// x rows hold the first halves [a1 (Ka) | g1 (Kg)] in fp32; CTA (x, y) owns 128 outputs of one of the two matrices and 16
+// tokens: the tokens' rows wait in shared memory rounded through the matrices' type, a thread owns one output for all 16 tokens
+// and streams its matrix row once in 16-byte pieces (every piece feeds 16 x 8 or 16 x 4 multiply-adds against broadcast reads).
+// The decay's outputs leave as exp(-exp(A_log[head]) softplus(. + dt_bias)), the gate's as they are.
+constexpr int kLrTokens = 16, kLrOut = 128;
+
+template <typename E>
+__global__ void __launch_bounds__(kLrOut) lowrank_pair_kernel(const float *__restrict__ x, int64_t ldx, int64_t T, const E *__restrict__ w_a, int64_t Na,
+                                                              int Ka, const E *__restrict__ w_g, int64_t Ng, int Kg, const float *__restrict__ A_log,
+                                                              const float *__restrict__ dt_bias, int D, float *__restrict__ a,
+                                                              float *__restrict__ g, int vec) {
+    extern __shared__ __align__(16) float lr_x[]; // [kLrTokens][Kp]
+    constexpr int VE = 16 / (int)sizeof(E);
+    const int blocks_a = (int)((Na + kLrOut - 1) / kLrOut);
+    const bool is_a = (int)blockIdx.x < blocks_a;
+    const int64_t n = (int64_t)(is_a ? blockIdx.x : blockIdx.x - blocks_a) * kLrOut + threadIdx.x, N = is_a ? Na : Ng;
+    const int K = is_a ? Ka : Kg, koff = is_a ? 0 : Ka, Kp = (K + 3) & ~3;
+    const int64_t t0 = (int64_t)blockIdx.y * kLrTokens;
+    const int nt = (int)min((int64_t)kLrTokens, T - t0);
+    for (int e = threadIdx.x; e < kLrTokens * Kp; e += blockDim.x) {
+        const int tt = e / Kp, k = e - tt * Kp;
+        lr_x[e] = (tt < nt && k < K) ? to_f32(from_f32<E>(x[(t0 + tt) * ldx + koff + k])) : 0.f;
+    }
+    __syncthreads();
+    if (n >= N) return;
+    const E *wr = (is_a ? w_a : w_g) + n * K;
+    float acc[kLrTokens];
+#pragma unroll
+    for (int tt = 0; tt < kLrTokens; tt++) acc[tt] = 0.f;
+    if (vec) { // K a multiple of the 16-byte piece, rows aligned
+        for (int k = 0; k < K; k += VE) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wr + k);
+            const E *we = reinterpret_cast<const E *>(&wv);
+            float wf[VE];
+#pragma unroll
+            for (int u = 0; u < VE; u++) wf[u] = to_f32(we[u]);
+#pragma unroll
+            for (int tt = 0; tt < kLrTokens; tt++) {
+#pragma unroll
+                for (int u = 0; u < VE; u += 4) {
+                    const float4 xv = *reinterpret_cast<const float4 *>(lr_x + tt * Kp + k + u);
+                    acc[tt] = fmaf(wf[u], xv.x, acc[tt]);
+                    acc[tt] = fmaf(wf[u + 1], xv.y, acc[tt]);
+                    acc[tt] = fmaf(wf[u + 2], xv.z, acc[tt]);
+                    acc[tt] = fmaf(wf[u + 3], xv.w, acc[tt]);
+                }
+            }
+        }
+    } else {
+        for (int k = 0; k < K; k++) {
+            const float wf = to_f32(wr[k]);
+#pragma unroll
+            for (int tt = 0; tt < kLrTokens; tt++) acc[tt] = fmaf(wf, lr_x[tt * Kp + k], acc[tt]);
+        }
+    }
+    if (is_a && A_log) {
+        const float rate = expf(A_log[n / D]), bias = dt_bias[n];
+#pragma unroll
+        for (int tt = 0; tt < kLrTokens; tt++) acc[tt] = expf(-rate * softplus_f32(acc[tt] + bias));
+    }
+    float *out = is_a ? a : g;
+#pragma unroll
+    for (int tt = 0; tt < kLrTokens; tt++)
+        if (tt < nt) out[(t0 + tt) * N + n] = acc[tt];
+}
+
 template <int DS, int CV, int MODE>
 int recurrence_launch_cv(const rec_args &p) {
     const dim3 grid((unsigned)p.H, (unsigned)((p.Dv + CV - 1) / CV));
@@ -354,12 +425,35 @@ int ggb_op_causal_conv_bias(int dt, const float *x, int64_t ldx, int64_t T, int6
     return GGB_OK;
 }
 
+int ggb_lowrank_pair_fits(int dt, int Ka, int Kg) { return (size_t)kLrTokens * (size_t)(std::max(Ka, Kg) + 3) * 4 <= 48 * 1024; }
+
+int ggb_op_lowrank_pair(int dt, const float *x, int64_t ldx, int64_t T, const void *w_a, int64_t Na, int Ka, const void *w_g, int64_t Ng, int Kg,
+                        const float *A_log, const float *dt_bias, int D, float *a, float *g) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_ARG(dt == GGB_TYPE_BF16 || dt == GGB_TYPE_F32, "lowrank_pair: dtype %d is neither bf16 nor f32", dt);
+    GGB_CHECK_ARG(x && w_a && w_g && a && g && T > 0 && Na > 0 && Ng > 0 && Ka > 0 && Kg > 0 && ldx >= Ka + Kg && (!A_log || (dt_bias && D > 0 && Na % D == 0)),
+                  "lowrank_pair: bad arguments");
+    GGB_CHECK_ARG(ggb_lowrank_pair_fits(dt, Ka, Kg), "lowrank_pair: inner sizes %d / %d do not fit shared memory", Ka, Kg);
+    const int ve = dt == GGB_TYPE_BF16 ? 8 : 4;
+    const int vec = Ka % ve == 0 && Kg % ve == 0 && (((uintptr_t)w_a | (uintptr_t)w_g) & 15) == 0;
+    const size_t smem = (size_t)kLrTokens * (size_t)((std::max(Ka, Kg) + 3) & ~3) * 4;
+    const dim3 grid((unsigned)((Na + kLrOut - 1) / kLrOut + (Ng + kLrOut - 1) / kLrOut), (unsigned)((T + kLrTokens - 1) / kLrTokens));
+    if (dt == GGB_TYPE_BF16)
+        lowrank_pair_kernel<<<grid, kLrOut, smem, ggb_cuda_stream()>>>(x, ldx, T, (const __nv_bfloat16 *)w_a, Na, Ka, (const __nv_bfloat16 *)w_g, Ng, Kg, A_log,
+                                                                      dt_bias, D, a, g, vec);
+    else
+        lowrank_pair_kernel<<<grid, kLrOut, smem, ggb_cuda_stream()>>>(x, ldx, T, (const float *)w_a, Na, Ka, (const float *)w_g, Ng, Kg, A_log, dt_bias, D, a, g,
+                                                                      vec);
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
 int ggb_op_lightning_attn(const float *q, const float *k, const float *v, int64_t ld, int64_t T, int H, int D, int Dv, const float *decay,
                           float *state, float *o, int64_t ldo) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_ARG(q && k && v && decay && state && o && T > 0 && H > 0 && D > 0 && D <= 64 * kNS && Dv > 0 && ldo >= (int64_t)H * Dv,
                   "lightning_attn: bad arguments (key size %d, at most %d)", D, 64 * kNS);
-    rec_args p{q, k, v, nullptr, nullptr, ld, 0, 0, T, H, H, D, Dv, decay, nullptr, nullptr, state, o, ldo};
+    rec_args p{q, k, v, nullptr, nullptr, ld, 0, 0, T, H, H, D, Dv, decay, nullptr, nullptr, state, o, ldo, 0};
     return recurrence_launch<0>(p);
 }
 
@@ -369,17 +463,18 @@ int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t l
     GGB_CHECK_ARG(q && k && v && b && a && A_log && dt_bias && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 64 * kNS &&
                       Dv > 0 && ldo >= (int64_t)H * Dv,
                   "gated_delta: bad arguments (heads %d over %d key heads, key size %d)", H, G, D);
-    rec_args p{q, k, v, b, a, ld, ld_ba, ld_ba, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
+    rec_args p{q, k, v, b, a, ld, ld_ba, ld_ba, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo, 0};
     return recurrence_launch<1>(p);
 }
 
 int ggb_op_channel_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, int64_t ld_b, const float *a, int64_t ld_a,
-                         int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo) {
+                         int decays, int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o,
+                         int64_t ldo) {
     GGB_REQUIRE_INIT();
-    GGB_CHECK_ARG(q && k && v && b && a && A_log && dt_bias && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 64 * kNS &&
-                      Dv > 0 && ldo >= (int64_t)H * Dv && ld_a >= (int64_t)H * D && ld_b >= H,
+    GGB_CHECK_ARG(q && k && v && b && a && (decays || (A_log && dt_bias)) && state && o && T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 &&
+                      D <= 64 * kNS && Dv > 0 && ldo >= (int64_t)H * Dv && ld_a >= (int64_t)H * D && ld_b >= H,
                   "channel_delta: bad arguments (heads %d over %d key heads, key size %d)", H, G, D);
-    rec_args p{q, k, v, b, a, ld, ld_b, ld_a, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo};
+    rec_args p{q, k, v, b, a, ld, ld_b, ld_a, T, H, G, D, Dv, nullptr, A_log, dt_bias, state, o, ldo, decays};
     return recurrence_launch<2>(p);
 }
 

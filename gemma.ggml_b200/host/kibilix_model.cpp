@@ -524,12 +524,18 @@ int kibilix_model::emit(int T, const int32_t *table, float *state, int n_want) {
             const int64_t GD = (int64_t)R.kv_heads * R.dim, HD = (int64_t)R.heads * R.dim, RV = (int64_t)R.heads * R.vdim, C = 2 * GD + RV;
             const int64_t LR = (int64_t)R.a_rank + R.g_rank;
             KB_OP("op_conv", ggb_op_causal_conv(dt_, pr_ + w.o_q, N, t, C, w.conv, R.conv, 0, 1, R.conv > 1 ? state + r.s_conv : nullptr, cv_, C, nullptr));
-            // the second halves of the two low-rank projections read the first halves in the matrices' type
-            KB_OP("op_act", ggb_op_act_rows(dt_, pr_ + w.o_a1, N, t, LR, 0, lr_));
-            KB_OP("op_linear", ggb_op_linear(dt_, w.a2, HD, R.a_rank, lr_, LR, t, da_, HD));
-            KB_OP("op_linear", ggb_op_linear(dt_, w.g2, RV, R.g_rank, (const char *)lr_ + (size_t)R.a_rank * es, LR, t, dg_, RV));
-            KB_OP("op_recurrence", ggb_op_channel_delta(cv_, cv_ + GD, cv_ + 2 * GD, C, pr_ + w.o_b, N, da_, HD, t, R.heads, R.kv_heads, R.dim, R.vdim,
-                                                        w.A_log, w.dt_bias, state + r.s_S, ro_, RV));
+            // the second halves of the two low-rank projections read the first halves in the matrices' type; the fused form
+            // hands the recurrence the decays themselves
+            const bool fused = ggb_lowrank_pair_fits(dt_, R.a_rank, R.g_rank) != 0;
+            if (fused) {
+                KB_OP("op_linear", ggb_op_lowrank_pair(dt_, pr_ + w.o_a1, N, t, w.a2, HD, R.a_rank, w.g2, RV, R.g_rank, w.A_log, w.dt_bias, R.dim, da_, dg_));
+            } else {
+                KB_OP("op_act", ggb_op_act_rows(dt_, pr_ + w.o_a1, N, t, LR, 0, lr_));
+                KB_OP("op_linear", ggb_op_linear(dt_, w.a2, HD, R.a_rank, lr_, LR, t, da_, HD));
+                KB_OP("op_linear", ggb_op_linear(dt_, w.g2, RV, R.g_rank, (const char *)lr_ + (size_t)R.a_rank * es, LR, t, dg_, RV));
+            }
+            KB_OP("op_recurrence", ggb_op_channel_delta(cv_, cv_ + GD, cv_ + 2 * GD, C, pr_ + w.o_b, N, da_, HD, fused ? 1 : 0, t, R.heads, R.kv_heads, R.dim,
+                                                        R.vdim, w.A_log, w.dt_bias, state + r.s_S, ro_, RV));
             KB_OP("op_norm", ggb_op_norm_gate(dt_, ro_, RV, dg_, RV, t, R.heads, R.vdim, w.onorm, R.vdim, c.eps, 0, gd_));
             KB_OP("op_linear", ggb_op_linear(dt_, w.o, W, RV, gd_, RV, t, ya_, W));
         }

@@ -338,7 +338,17 @@ int ggb_op_gated_delta(const float *q, const float *k, const float *v, int64_t l
  * b [T][H] (row stride ld_b); g[h][d] = exp(-exp(A_log[h]) softplus(a[h][d] + dt_bias[h][d])) multiplies row d of the head's
  * S [D][Dv] before the token's write; everything else as ggb_op_gated_delta */
 int ggb_op_channel_delta(const float *q, const float *k, const float *v, int64_t ld, const float *b, int64_t ld_b, const float *a, int64_t ld_a,
-                         int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o, int64_t ldo);
+                         int decays, int64_t T, int H, int G, int D, int Dv, const float *A_log, const float *dt_bias, float *state, float *o,
+                         int64_t ldo);
+/* decays 1 above: `a` already holds g (A_log and dt_bias unused), e.g. from the operator below.
+ * The second halves of two low-rank projections in one launch: x rows = [a1 (Ka) | g1 (Kg)] fp32 (row stride ldx), rounded
+ * to dt on the way in; a[t][n] = w_a[n] . a1[t] (Na outputs, w_a [Na][Ka] in dt) and g[t][n] = w_g[n] . g1[t] (Ng outputs), fp32,
+ * dense.  With A_log (then dt_bias [Na], heads of D outputs): a leaves as exp(-exp(A_log[n / D]) softplus(a + dt_bias[n])), the
+ * decays of ggb_op_channel_delta.  ggb_lowrank_pair_fits: 0 when the inner sizes are too large for the kernel's shared memory
+ * (callers then use ggb_op_act_rows and ggb_op_linear). */
+int ggb_lowrank_pair_fits(int dt, int Ka, int Kg);
+int ggb_op_lowrank_pair(int dt, const float *x, int64_t ldx, int64_t T, const void *w_a, int64_t Na, int Ka, const void *w_g, int64_t Ng, int Kg,
+                        const float *A_log, const float *dt_bias, int D, float *a, float *g);
 
 /* ------------------------------------------------------------------ sliding-window attention (csrc/window_attention.cu)
  * Grouped-query soft-max attention over a paged cache whose row per position is [k (G * D) | v (G * Dv)] in dt,

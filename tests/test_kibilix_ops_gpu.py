@@ -242,7 +242,7 @@ def delta_want(q, k, v, b, a, A_log, dt_bias, H, G, D, Dv):
     return KP.channel_delta_core(qq, kk, v.reshape(T, H, Dv), KP.sigmoid(b), g)
 
 
-def run_delta(gpu, q, k, v, b, a, A_log, dt_bias, H, G, D, Dv, cuts, ld_extra=3):
+def run_delta(gpu, q, k, v, b, a, A_log, dt_bias, H, G, D, Dv, cuts, ld_extra=3, decays=0):
     lib = gpu.cuda_lib()
     T = q.shape[0]
     rows = f32(np.concatenate([q, k, v, np.zeros((T, ld_extra))], 1))   # a row stride of its own
@@ -253,7 +253,7 @@ def run_delta(gpu, q, k, v, b, a, A_log, dt_bias, H, G, D, Dv, cuts, ld_extra=3)
     for c in cuts:
         xr, bb, aa, o = dev(gpu, rows[lo:lo + c]), dev(gpu, f32(b[lo:lo + c])), dev(gpu, f32(a[lo:lo + c])), zeros(gpu, c * H * Dv * 4)
         p = xr.ptr.value
-        gpu.check(lib.ggb_op_channel_delta(p, p + 4 * G * D, p + 8 * G * D, ld, bb.ptr, H, aa.ptr, H * D, c, H, G, D, Dv, Al.ptr, db.ptr, state.ptr, o.ptr, H * Dv),
+        gpu.check(lib.ggb_op_channel_delta(p, p + 4 * G * D, p + 8 * G * D, ld, bb.ptr, H, aa.ptr, H * D, decays, c, H, G, D, Dv, Al.ptr, db.ptr, state.ptr, o.ptr, H * Dv),
                   "channel_delta")
         got.append(o.download(np.float32, c * H * Dv).reshape(c, H, Dv))
         lo += c
@@ -287,6 +287,38 @@ def test_a_channel_that_forgets_at_once_keeps_nothing_and_its_neighbours_keep_al
     assert F.rel_err(got, want) < 5e-6 and F.rel_err(state, S) < 5e-6
     kk = KP.unit(k.reshape(T, G, D))[-1, 0]
     assert np.abs(state[0, 2]).max() <= np.abs(kk[2]) * np.abs(v).max() * 4 and np.abs(state[0, 1]).max() > 0
+
+
+@pytest.mark.parametrize("dt", [F32, BF16])
+@pytest.mark.parametrize("Ka,Kg,H,D,Dv,T", [(6, 7, 4, 12, 5, 5), (24, 24, 4, 64, 64, 37), (64, 64, 2, 128, 128, 1), (9, 130, 3, 7, 9, 16), (8, 16, 5, 40, 52, 17)])
+def test_low_rank_pair_gives_the_decays_and_the_gate_rows(gpu, dt, Ka, Kg, H, D, Dv, T):
+    r = np.random.default_rng(Ka + T)
+    lib = gpu.cuda_lib()
+    x = f32(r.standard_normal((T, Ka + Kg + 3)))
+    (wav, wau), (wgv, wgu) = as_dt(dt, r.standard_normal((H * D, Ka))), as_dt(dt, r.standard_normal((H * Dv, Kg)) / np.sqrt(Kg))
+    A_log, dt_bias = -1.0 + r.standard_normal(H), r.standard_normal(H * D)
+    xa, xg = as_dt(dt, x[:, :Ka])[0], as_dt(dt, x[:, Ka:Ka + Kg])[0]
+    want_a = np.exp(-np.exp(A_log)[None, :, None] * KP.softplus(xa @ wav.T + dt_bias).reshape(T, H, D)).reshape(T, H * D)
+    want_g = xg @ wgv.T
+    assert lib.ggb_lowrank_pair_fits(dt, Ka, Kg) == 1 and lib.ggb_lowrank_pair_fits(dt, 4000, Kg) == 0
+    a, g = zeros(gpu, T * H * D * 4), zeros(gpu, T * H * Dv * 4)
+    gpu.check(lib.ggb_op_lowrank_pair(dt, dev(gpu, x).ptr, x.shape[1], T, dev(gpu, wau).ptr, H * D, Ka, dev(gpu, wgu).ptr, H * Dv, Kg, dev(gpu, f32(A_log)).ptr,
+                                      dev(gpu, f32(dt_bias)).ptr, D, a.ptr, g.ptr), "lowrank_pair")
+    assert F.rel_err(a.download(np.float32, T * H * D).reshape(T, -1), want_a) < 5e-6
+    assert F.rel_err(g.download(np.float32, T * H * Dv).reshape(T, -1), want_g) < 5e-6
+    # without the decay's constants both outputs are plain products
+    gpu.check(lib.ggb_op_lowrank_pair(dt, dev(gpu, x).ptr, x.shape[1], T, dev(gpu, wau).ptr, H * D, Ka, dev(gpu, wgu).ptr, H * Dv, Kg, None, None, 0, a.ptr, g.ptr),
+              "lowrank_pair")
+    assert F.rel_err(a.download(np.float32, T * H * D).reshape(T, -1), xa @ wav.T) < 5e-6
+
+
+def test_the_recurrence_takes_ready_decays_as_well_as_raw_rows(gpu):
+    H, G, D, Dv, T = 3, 1, 20, 6, 40
+    q, k, v, b, a, A_log, dt_bias = delta_inputs(np.random.default_rng(6), T, H, G, D, Dv)
+    want, S = delta_want(q, k, v, b, a, A_log, dt_bias, H, G, D, Dv)
+    g = np.exp(-np.exp(A_log)[None, :, None] * KP.softplus(a + dt_bias).reshape(T, H, D)).reshape(T, H * D)
+    got, state = run_delta(gpu, q, k, v, b, g, A_log * 0 + 99, dt_bias * 0 + 99, H, G, D, Dv, [7, 1, 32], decays=1)
+    assert F.rel_err(got, want) < 5e-6 and F.rel_err(state, S) < 5e-6
 
 
 # ------------------------------------------------------------------------------------------------ router and identity experts
