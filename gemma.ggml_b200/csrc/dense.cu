@@ -784,13 +784,13 @@ constexpr int kMaxStreams = 16;
 //   in_w: u = sum_s in_w[s] x_s is read out, as fp32 (u_out) and / or normed, u / sqrt(mean(u^2) + eps) * nw, in dt (h)
 // With `rows` the CTA's token is rows[blockIdx.x] and nothing is written back to xs (a few rows read out at the end: what y
 // brings enters on the way).
-template <typename E, int SM, int V>
-__global__ void __launch_bounds__(256) hyper_mix_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y,
+template <typename E, int SM, int V, int TB>
+__global__ void __launch_bounds__(TB) hyper_mix_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y,
                                                         const float *__restrict__ mix, const float *__restrict__ coef, int S,
                                                         const float *__restrict__ in_w, const float *__restrict__ nw, float eps, int64_t W,
                                                         const int32_t *__restrict__ rows, float *__restrict__ u_out, E *__restrict__ h) {
     extern __shared__ __align__(16) float hm_row[]; // [W] the read-out u
-    __shared__ float red[8], s_mix[SM * SM], s_coef[SM], s_in[SM];
+    __shared__ float red[32], s_mix[SM * SM], s_coef[SM], s_in[SM];
     const int64_t b = blockIdx.x, t = rows ? rows[b] : b;
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[(i / S) * SM + i % S] = mix ? mix[i] : 0.f;
     if ((int)threadIdx.x < S) {
@@ -865,7 +865,7 @@ __global__ void __launch_bounds__(256) hyper_mix_kernel(float *xs, const float *
         }
     }
     if (!h) return;
-    const float r = 1.0f / sqrtf(block_sum_256(ss, red) / (float)W + eps);
+    const float r = 1.0f / sqrtf(block_sum_any(ss, red) / (float)W + eps);
     for (int64_t i = (int64_t)threadIdx.x * V; i < W; i += (int64_t)blockDim.x * V) // a thread reads what it wrote
 #pragma unroll
         for (int c = 0; c < V; c++) h[b * W + i + c] = from_f32<E>(hm_row[i + c] * r * nw[i + c]);
@@ -894,17 +894,21 @@ int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const f
     GGB_CHECK_ARG((!y || (mix && coef)) && (!(u_out || h) || in_w) && (!h || nw), "hyper_mix: an input without its weights");
     const size_t smem = h ? (size_t)W * 4 : 0;
     GGB_CHECK_ARG(smem <= 200 * 1024, "hyper_mix: width %lld does not fit shared memory", (long long)W);
-    // 16-byte pieces need rows that start on one (up to 8 streams: the wider forms keep the registers of one column)
-    const bool vec = W % 4 == 0 && S <= 8 && (((uintptr_t)xs | (uintptr_t)x0 | (uintptr_t)y) & 15) == 0;
+    // 16-byte pieces need rows that start on one (up to 4 streams: the wider forms keep the registers of one column)
+    const bool vec = W % 4 == 0 && S <= 4 && (((uintptr_t)xs | (uintptr_t)x0 | (uintptr_t)y) & 15) == 0;
+    // a step of few tokens is a chain of latencies on a nearly empty GPU: a wide CTA covers the row in one pass
+    const int64_t per_pass = W / (vec ? 4 : 1);
+    const bool wide = T <= 64 && per_pass >= 512 && S <= 4; // 512 threads: these forms keep their registers
 #define HM_LAUNCH_V(ET, SM, V)                                                                                                \
     {                                                                                                                          \
-        auto k = hyper_mix_kernel<ET, SM, V>;                                                                                  \
+        auto k = hyper_mix_kernel<ET, SM, V, 256>;                                                                             \
+        if (SM <= 4 && wide) k = hyper_mix_kernel<ET, (SM <= 4 ? SM : 4), V, 512>;                                             \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
-        k<<<(unsigned)T, 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h);      \
+        k<<<(unsigned)T, wide ? 512 : 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h); \
     }
 #define HM_LAUNCH(ET, SM)                       \
     {                                           \
-        if (vec && SM <= 8) HM_LAUNCH_V(ET, (SM <= 8 ? SM : 8), 4) \
+        if (vec && SM <= 4) HM_LAUNCH_V(ET, (SM <= 4 ? SM : 4), 4) \
         else HM_LAUNCH_V(ET, SM, 1)             \
     }
 #define HM_S(ET)                              \
