@@ -1022,12 +1022,12 @@ def kibilix_config(size):
             mx = {"heads": Hr, "kv_heads": Gr, "dim": D, "vdim": D, "conv": 4, "rank": KB_RANK}
             kind = "channel_delta"
         else:
-            mx = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 50.0, "mask": {"size": chunk},
+            mx = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0, "mask": {"size": chunk},
                   "rot": {"base": 500000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
             kind = "attention"
         mlp = {"kind": "dense", "ff": ff} if i % 4 < 2 else {"kind": "moe", "expert": {"ff": eff, "limit": 7.0}, "router": {"experts": E, "identity": I, "top": top}}
         layers.append({"type": kind, "mixer": mx, "mlp": mlp})
-    return {"architecture": "Kibilix", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": KB_STREAMS,
+    return {"architecture": "Kibilix", "vocab": V, "width": W, "norm": {"eps": 1e-5}, "residual_mult": 0.7, "streams": KB_STREAMS,
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 31}}, "layers": layers}
 
 

@@ -194,10 +194,10 @@ def test_a_far_token_reaches_the_end_through_the_delta_rule_only(gpu, tmp_path):
 
 
 def test_random_weight_engine_portions_agree_at_sizes_that_reach_the_tensor_cores(gpu):
-    cfg = F.config([F.layer("channel_delta", F.delta(heads=4, kv_heads=2, dim=64, vdim=64, conv=4), F.moe(experts=8, identity=1, top=2, ff=128, limit=7.0)),
+    cfg = F.config([F.layer("channel_delta", F.delta(heads=6, kv_heads=2, dim=64, vdim=32, conv=3), F.moe(experts=6, identity=1, top=2, ff=128, limit=7.0)),
                     F.layer("attention", F.attention(heads=8, kv_heads=2, dim=64, vdim=64, chunk=100, dims=32), F.dense(512))],
-                   vocab=512, width=256, streams=4, buckets=509, loop=(0, 2, 2))
-    toks = np.random.default_rng(0).integers(0, 512, 400)
+                   vocab=500, width=384, streams=3, buckets=251, loop=(0, 2, 2))
+    toks = np.random.default_rng(0).integers(0, 500, 400)
     for dtype in ("bfloat16", "float32"):
         eng = gpu.Engine(config=cfg, seed=7, dtype=dtype, max_tokens=1024)
         whole = eng.step([("w", toks, np.arange(400))], ["w"])
