@@ -777,10 +777,22 @@ int ggb_norm_add_norm_launch(int dt, const float *a, const float *bias, const in
 namespace {
 
 constexpr int kMaxStreams = 16;
+constexpr int kMaxHyperTop = 64;
+
+// a sublayer's output that is still the slot rows of a mixture of experts: y[t] = sum_k wt[t][k] (slot k's row of y2, or the
+// token's row of h_in where the slot's expert is an identity expert: idx >= n_real)
+template <typename E> struct hyper_slots {
+    const float *y2 = nullptr;
+    const int32_t *inv = nullptr, *idx = nullptr;
+    const float *wt = nullptr;
+    int top = 0, n_real = 0;
+    const E *h_in = nullptr; // may be the buffer h is written to: a thread reads its columns before it writes them
+};
 
 // One CTA per row.  The residual is S streams x_1 .. x_S per token ([T][S][W] fp32).  In one pass over the token's columns:
 //   x0:   every stream starts as the row of x0 (the embedding output) instead of what xs holds
 //   y:    the sublayer's output enters, all streams at once from the old ones: x_t <- sum_s mix[s][t] x_s + coef[t] y
+//         (or sl: the output is summed from its expert slots on the way in)
 //   in_w: u = sum_s in_w[s] x_s is read out, as fp32 (u_out) and / or normed, u / sqrt(mean(u^2) + eps) * nw, in dt (h)
 // With `rows` the CTA's token is rows[blockIdx.x] and nothing is written back to xs (a few rows read out at the end: what y
 // brings enters on the way).
@@ -788,10 +800,17 @@ template <typename E, int SM, int V, int TB>
 __global__ void __launch_bounds__(TB) hyper_mix_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y,
                                                         const float *__restrict__ mix, const float *__restrict__ coef, int S,
                                                         const float *__restrict__ in_w, const float *__restrict__ nw, float eps, int64_t W,
-                                                        const int32_t *__restrict__ rows, float *__restrict__ u_out, E *__restrict__ h) {
+                                                        const int32_t *__restrict__ rows, float *__restrict__ u_out, E *h, hyper_slots<E> sl) {
     extern __shared__ __align__(16) float hm_row[]; // [W] the read-out u
-    __shared__ float red[32], s_mix[SM * SM], s_coef[SM], s_in[SM];
+    __shared__ float red[32], s_mix[SM * SM], s_coef[SM], s_in[SM], s_wt[kMaxHyperTop];
+    __shared__ int64_t s_row[kMaxHyperTop];
     const int64_t b = blockIdx.x, t = rows ? rows[b] : b;
+    const bool renew = y || sl.y2;
+    if (sl.y2 && (int)threadIdx.x < sl.top) { // the token's slots, looked up once
+        const int64_t k = t * sl.top + threadIdx.x;
+        s_wt[threadIdx.x] = sl.wt[k];
+        s_row[threadIdx.x] = sl.idx[k] < sl.n_real ? (int64_t)sl.inv[k] * W : -1;
+    }
     for (int i = threadIdx.x; i < S * S; i += blockDim.x) s_mix[(i / S) * SM + i % S] = mix ? mix[i] : 0.f;
     if ((int)threadIdx.x < S) {
         s_coef[threadIdx.x] = coef ? coef[threadIdx.x] : 0.f;
@@ -818,8 +837,29 @@ __global__ void __launch_bounds__(TB) hyper_mix_kernel(float *xs, const float *_
                 for (int c = 0; c < V; c++) x[s][c] = 0.f;
             }
         }
-        if (y) {
-            if (V == 4) {
+        if (renew) {
+            if (sl.y2) {
+#pragma unroll
+                for (int c = 0; c < V; c++) yv[c] = 0.f;
+                for (int k = 0; k < sl.top; k++) {
+                    const float w = s_wt[k];
+                    float sv[V];
+                    if (s_row[k] >= 0) {
+                        const float *src = sl.y2 + s_row[k] + i;
+                        if (V == 4) {
+                            const float4 v4 = *reinterpret_cast<const float4 *>(src);
+                            sv[0] = v4.x, sv[1 % V] = v4.y, sv[2 % V] = v4.z, sv[3 % V] = v4.w;
+                        } else {
+                            sv[0] = src[0];
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < V; c++) sv[c] = to_f32(sl.h_in[t * W + i + c]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < V; c++) yv[c] = fmaf(w, sv[c], yv[c]);
+                }
+            } else if (V == 4) {
                 const float4 v4 = *reinterpret_cast<const float4 *>(y + t * W + i);
                 yv[0] = v4.x, yv[1 % V] = v4.y, yv[2 % V] = v4.z, yv[3 % V] = v4.w;
             } else {
@@ -841,7 +881,7 @@ __global__ void __launch_bounds__(TB) hyper_mix_kernel(float *xs, const float *_
 #pragma unroll
                 for (int c = 0; c < V; c++) x[s][c] = n[s][c];
         }
-        if ((y || x0) && !rows) {
+        if ((renew || x0) && !rows) {
 #pragma unroll
             for (int s = 0; s < SM; s++)
                 if (s < S) {
@@ -886,25 +926,29 @@ __global__ void act_rows_kernel(const float *__restrict__ x, int64_t ldx, int64_
 
 extern "C" {
 
-int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const float *mix, const float *coef, int S, const float *in_w,
-                     const float *nw, float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h) {
+static int hyper_mix_launch(int dt, float *xs, const float *x0, const float *y, const float *y2, const int32_t *inv, const float *wt, const int32_t *idx,
+                            int top, int n_real, const void *h_in, const float *mix, const float *coef, int S, const float *in_w, const float *nw,
+                            float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h) {
     GGB_REQUIRE_INIT();
     GGB_CHECK_DT(dt);
     GGB_CHECK_ARG(xs && W > 0 && T > 0 && S > 0 && S <= kMaxStreams, "hyper_mix: bad arguments (%d streams, at most %d)", S, kMaxStreams);
-    GGB_CHECK_ARG((!y || (mix && coef)) && (!(u_out || h) || in_w) && (!h || nw), "hyper_mix: an input without its weights");
+    GGB_CHECK_ARG((!(y || y2) || (mix && coef)) && (!(u_out || h) || in_w) && (!h || nw) && !(y && y2), "hyper_mix: an input without its weights");
+    GGB_CHECK_ARG(!y2 || (inv && wt && idx && h_in && top > 0 && top <= kMaxHyperTop), "hyper_mix: expert slots without their lists (at most %d a token)", kMaxHyperTop);
     const size_t smem = h ? (size_t)W * 4 : 0;
     GGB_CHECK_ARG(smem <= 200 * 1024, "hyper_mix: width %lld does not fit shared memory", (long long)W);
     // 16-byte pieces need rows that start on one (up to 4 streams: the wider forms keep the registers of one column)
-    const bool vec = W % 4 == 0 && S <= 4 && (((uintptr_t)xs | (uintptr_t)x0 | (uintptr_t)y) & 15) == 0;
+    const bool vec = W % 4 == 0 && S <= 4 && (((uintptr_t)xs | (uintptr_t)x0 | (uintptr_t)y | (uintptr_t)y2) & 15) == 0;
     // a step of few tokens is a chain of latencies on a nearly empty GPU: a wide CTA covers the row in one pass
     const int64_t per_pass = W / (vec ? 4 : 1);
     const bool wide = T <= 64 && per_pass >= 512 && S <= 4; // 512 threads: these forms keep their registers
 #define HM_LAUNCH_V(ET, SM, V)                                                                                                \
     {                                                                                                                          \
+        hyper_slots<ET> sl;                                                                                                    \
+        sl.y2 = y2, sl.inv = inv, sl.idx = idx, sl.wt = wt, sl.top = top, sl.n_real = n_real, sl.h_in = (const ET *)h_in;       \
         auto k = hyper_mix_kernel<ET, SM, V, 256>;                                                                             \
         if (SM <= 4 && wide) k = hyper_mix_kernel<ET, (SM <= 4 ? SM : 4), V, 512>;                                             \
         if (smem > 48 * 1024) GGB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));        \
-        k<<<(unsigned)T, wide ? 512 : 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h); \
+        k<<<(unsigned)T, wide ? 512 : 256, smem, ggb_cuda_stream()>>>(xs, x0, y, mix, coef, S, in_w, nw, eps, W, rows, u_out, (ET *)h, sl); \
     }
 #define HM_LAUNCH(ET, SM)                       \
     {                                           \
@@ -925,6 +969,19 @@ int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const f
 #undef HM_LAUNCH_V
     GGB_LAUNCH_CHECK();
     return GGB_OK;
+}
+
+int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const float *mix, const float *coef, int S, const float *in_w,
+                     const float *nw, float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h) {
+    return hyper_mix_launch(dt, xs, x0, y, nullptr, nullptr, nullptr, nullptr, 0, 0, nullptr, mix, coef, S, in_w, nw, eps, W, T, rows, u_out, h);
+}
+
+int ggb_op_hyper_mix_moe(int dt, float *xs, const float *y2, const int32_t *ws, const float *wt, const int32_t *idx, int64_t T_slots, int top, int n_exp,
+                         int n_identity, const void *h_in, const float *mix, const float *coef, int S, const float *in_w, const float *nw, float eps,
+                         int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h) {
+    GGB_CHECK_ARG(ws && top > 0 && n_exp > 0 && n_identity >= 0 && n_identity <= n_exp && T_slots >= T, "hyper_mix_moe: bad arguments");
+    return hyper_mix_launch(dt, xs, nullptr, nullptr, y2, ws + n_exp + 1 + T_slots * top, wt, idx, top, n_exp - n_identity, h_in, mix, coef, S, in_w, nw, eps, W, T,
+                            rows, u_out, h);
 }
 
 int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y) {

@@ -495,12 +495,18 @@ int kibilix_model::emit(int T, const int32_t *table, float *state, int n_want) {
         KB_OP("op_rows", ggb_op_embed_rows(dt_, embed_, ids_, t, W, x0_));
     // a sublayer's output waits for the next pass over the streams: that pass renews them and reads the next sublayer's
     // input out in one launch
+    // (experts: their weighted sum is taken in that launch too, from the slot rows)
     const float *start = x0_, *y = nullptr;
     const kb_hyper_w *from = nullptr;
+    const kb_moe_cfg *slots = nullptr;
     auto streams = [&](const float *in, const float *nw, const int32_t *rows, int64_t n, float *u_out, void *h) -> int {
-        KB_OP("op_residual", ggb_op_hyper_mix(dt_, xs_, start, y, from ? from->mix : nullptr, from ? from->coef : nullptr, S_, in, nw, c.eps, W, n,
-                                              rows, u_out, h));
-        start = nullptr, y = nullptr, from = nullptr;
+        if (slots)
+            KB_OP("op_residual", ggb_op_hyper_mix_moe(dt_, xs_, y2_, group_ws_, route_w_, route_i_, t, slots->top, slots->experts + slots->identity,
+                                                      slots->identity, h_, from->mix, from->coef, S_, in, nw, c.eps, W, n, rows, u_out, h));
+        else
+            KB_OP("op_residual", ggb_op_hyper_mix(dt_, xs_, start, y, from ? from->mix : nullptr, from ? from->coef : nullptr, S_, in, nw, c.eps, W, n,
+                                                  rows, u_out, h));
+        start = nullptr, y = nullptr, from = nullptr, slots = nullptr;
         return 0;
     };
     for (size_t ri = 0; ri < runs_.size(); ri++) {
@@ -563,7 +569,8 @@ int kibilix_model::emit(int T, const int32_t *table, float *state, int n_want) {
                 }
                 KB_OP("op_moe_linear", ggb_op_moe_linear_identity(dt_, w.e_down, W, E.ff, act_, E.ff, 0, t, E.top, all, E.identity, group_ws_, 0, 0.f, 0.f,
                                                                   y2_, W));
-                KB_OP("op_moe", ggb_op_moe_combine_identity(dt_, y2_, group_ws_, route_w_, route_i_, t, E.top, all, E.identity, W, h_, yb_));
+                if (E.top <= 64) slots = &E; // the weighted sum waits for the next pass over the streams
+                else KB_OP("op_moe", ggb_op_moe_combine_identity(dt_, y2_, group_ws_, route_w_, route_i_, t, E.top, all, E.identity, W, h_, yb_));
             }
             y = yb_, from = &w.hc2;
         }

@@ -307,6 +307,13 @@ int ggb_op_norm_add_norm(int dt, const float *a, const float *bias, const float 
  * enters on the way.  One stream with mix = in_w = {1} is the plain residual sum. */
 int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const float *mix, const float *coef, int S, const float *in_w,
                      const float *nw, float eps, int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h);
+/* the same where the sublayer was a mixture of experts whose weighted sum has not been taken yet: y[t] = sum_k wt[t][k] *
+ * (row of slot k in y2, or the token's row of h_in (dt, what the experts read) where idx[t][k] is an identity expert); ws, wt,
+ * idx, n_exp, n_identity as for ggb_op_moe_combine_identity, T_slots the number of tokens the slot lists were made for (with
+ * rows, T counts the rows read out).  h_in may be the buffer h is written to.  At most 64 slots a token. */
+int ggb_op_hyper_mix_moe(int dt, float *xs, const float *y2, const int32_t *ws, const float *wt, const int32_t *idx, int64_t T_slots, int top, int n_exp,
+                         int n_identity, const void *h_in, const float *mix, const float *coef, int S, const float *in_w, const float *nw, float eps,
+                         int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h);
 /* y (dt, dense [T][F]) = act(x), x fp32 rows of stride ldx; act 0: as it is, 1: relu(x)^2 */
 int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y);
 

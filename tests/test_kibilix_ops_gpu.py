@@ -322,7 +322,7 @@ def test_the_recurrence_takes_ready_decays_as_well_as_raw_rows(gpu):
 
 
 # ------------------------------------------------------------------------------------------------ router and identity experts
-def run_moe(gpu, dt, h, W, p, f, T):
+def run_moe(gpu, dt, h, W, p, f, T, streams=None):
     """router -> groups -> gate | up -> clamped gate -> down -> weighted sum with identity slots, as the model calls them"""
     lib = gpu.cuda_lib()
     r = f["router"]
@@ -353,6 +353,13 @@ def run_moe(gpu, dt, h, W, p, f, T):
         gpu.check(lib.ggb_op_glu_clamp(dt, gu_o.ptr, FF, n, lim, 1.702, act.ptr), "glu")
     gpu.check(lib.ggb_op_moe_linear_identity(dt, dnd.ptr, Wd, FF, act.ptr, FF, 0, T, top, E + I, I, ws.ptr, 0, 0.0, 0.0, y2.ptr, Wd), "down")
     gpu.check(lib.ggb_op_moe_combine_identity(dt, y2.ptr, ws.ptr, wt.ptr, idx.ptr, T, top, E + I, I, Wd, hd.ptr, out.ptr), "combine")
+    if streams is not None:  # the weighted sum taken inside the pass over the residual streams instead, h written over the experts' input
+        S, xs0, mix, coef, w_in, nw = streams
+        xs = dev(gpu, f32(xs0.transpose(1, 0, 2)))
+        gpu.check(lib.ggb_op_hyper_mix_moe(dt, xs.ptr, y2.ptr, ws.ptr, wt.ptr, idx.ptr, T, top, E + I, I, hd.ptr, dev(gpu, f32(mix)).ptr, dev(gpu, f32(coef)).ptr, S,
+                                           dev(gpu, f32(w_in)).ptr, dev(gpu, f32(nw)).ptr, 1e-5, Wd, T, None, None, hd.ptr), "hyper_mix_moe")
+        streams.append(xs.download(np.float32, T * S * Wd).reshape(T, S, Wd).transpose(1, 0, 2))
+        streams.append(from_dt(dt, hd, (T, Wd)))
     return (out.download(np.float32, T * Wd).reshape(T, Wd), idx.download(np.int32, n).reshape(T, top), wt.download(np.float32, n).reshape(T, top),
             KP.moe_ff(hv, Wq, p, f), hv)
 
@@ -366,13 +373,19 @@ def test_router_experts_and_identity_experts(gpu, dt, E, I, top, FF, Wd, T):
     cfg = F.config([F.layer("attention", F.attention(), f)], width=Wd, streams=0)
     W = KP.random_weights(cfg, seed=T)
     h = r.standard_normal((T, Wd))
-    got, idx, wt, want, hv = run_moe(gpu, dt, h, W, "l0.mlp.", f, T)
+    S = 1 + E % 4
+    st = [S, r.standard_normal((S, T, Wd)), np.eye(S) + 0.2 * r.standard_normal((S, S)), r.standard_normal(S), r.standard_normal(S), 1 + 0.1 * r.standard_normal(Wd)]
+    got, idx, wt, want, hv = run_moe(gpu, dt, h, W, "l0.mlp.", f, T, streams=st)
     widx, wwt = KP.route(hv, W["l0.mlp.router"].astype(np.float32).astype(np.float64), W["l0.mlp.correction"].astype(np.float32).astype(np.float64), top)
     same = (idx == widx).all(-1)
     assert same.mean() > 0.95  # a close call of two choice scores may fall the other way in fp32
     assert np.abs(wt[same] - wwt[same]).max() < 1e-5 and np.abs(wt.sum(-1) - 1).max() < 1e-5
     assert (idx >= E).any() == (I > 0 and top * T > 8) or I == 0 or top * T <= 8
     assert F.rel_err(got[same], want[same]) < (1.5e-2 if dt == BF16 else 1e-5)
+    # the same sum folded into the pass over the streams: the streams renewed from the separate sum, and the next input read out
+    new = KP.streams_write(st[1], got.astype(np.float64), st[2], st[3], 1.0)
+    assert F.rel_err(st[6], new) < 5e-6
+    assert F.rel_err(st[7], KP.rms_norm(KP.streams_read(new, st[4]), st[5], 1e-5)) < (1e-2 if dt == BF16 else 1e-5)
 
 
 def test_the_correction_changes_the_choice_and_not_the_weights_and_identity_hands_the_input_through(gpu):
