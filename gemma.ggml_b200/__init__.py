@@ -181,6 +181,7 @@ _CUDA_SIG = {
     "ggb_op_moe_combine_identity": (i32, [i32, vp, vp, vp, vp, i64, i32, i32, i32, i64, vp, vp]),
     "ggb_op_hyper_mix": (i32, [i32, vp, vp, vp, vp, vp, i32, vp, vp, f32, i64, i64, vp, vp, vp]),
     "ggb_op_act_rows": (i32, [i32, vp, i64, i64, i64, i32, vp]),
+    "ggb_op_linear_relu2": (i32, [i32, vp, i64, i64, vp, i64, i64, vp, vp]),
     "ggb_op_hyper_mix_moe": (i32, [i32, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp, vp, vp, i32, vp, vp, f32, i64, i64, vp, vp, vp]),
     "ggb_comm_unique_id": (i32, [vp]), "ggb_comm_init": (i32, [vp, i32, i32]), "ggb_comm_destroy": (i32, []),
     "ggb_comm_rank": (i32, []), "ggb_comm_size": (i32, []), "ggb_op_allgather": (i32, [vp, vp, sz]),

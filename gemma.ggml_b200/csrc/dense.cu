@@ -19,9 +19,10 @@ namespace {
 // 16-byte loads and keeps T accumulators.  HBM-bound (decode).
 constexpr int kVecT = 8;
 
-template <typename E, int TT>
+// ACT 1: the output is relu(.)^2 in the matrices' type (c_act) instead of fp32 (c)
+template <typename E, int TT, int ACT = 0>
 __global__ void __launch_bounds__(256) linear_vec_kernel(const E *__restrict__ w, int64_t N, int64_t K, const E *__restrict__ a,
-                                                         int64_t lda, float *__restrict__ c, int64_t ldc) {
+                                                         int64_t lda, float *__restrict__ c, int64_t ldc, E *__restrict__ c_act = nullptr) {
     constexpr int VE = 16 / (int)sizeof(E); // elements per 16-byte load
     const int lane = threadIdx.x & 31;
     const int64_t n = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -58,7 +59,10 @@ __global__ void __launch_bounds__(256) linear_vec_kernel(const E *__restrict__ w
 #pragma unroll
     for (int t = 0; t < TT; t++) {
         const float s = warp_sum_f32(acc[t]);
-        if (lane == 0) c[t * ldc + n] = s;
+        if (lane == 0) {
+            if (ACT == 1) c_act[t * ldc + n] = from_f32<E>(s > 0.f ? s * s : 0.f);
+            else c[t * ldc + n] = s;
+        }
     }
 }
 
@@ -331,6 +335,25 @@ int linear_launch(const E *w, int64_t N, int64_t K, const E *a, int64_t lda, int
     } else {
         const dim3 grid((unsigned)((N + 63) / 64), (unsigned)((T + 63) / 64));
         linear_tile_kernel<E, false, 0><<<grid, 256, 0, st>>>(w, N, K, a, lda, T, c, nullptr, ldc, ggb_moe_groups{});
+    }
+    GGB_LAUNCH_CHECK();
+    return GGB_OK;
+}
+
+// y (E, [T][N]) = relu(a W^T)^2 in one launch: the mat-vec or the tile kernel with the activation as its epilogue
+template <typename E>
+int linear_relu2_launch(const E *w, int64_t N, int64_t K, const E *a, int64_t lda, int64_t T, E *y) {
+    cudaStream_t st = ggb_cuda_stream();
+    if (T <= kVecT) {
+        const dim3 grid((unsigned)((N + 7) / 8));
+        switch ((int)T) {
+#define VEC_CASE(TT) case TT: linear_vec_kernel<E, TT, 1><<<grid, 256, 0, st>>>(w, N, K, a, lda, nullptr, N, y); break;
+            VEC_CASE(1) VEC_CASE(2) VEC_CASE(3) VEC_CASE(4) VEC_CASE(5) VEC_CASE(6) VEC_CASE(7) VEC_CASE(8)
+#undef VEC_CASE
+        }
+    } else {
+        const dim3 grid((unsigned)((N + 63) / 64), (unsigned)((T + 63) / 64));
+        linear_tile_kernel<E, false, 1><<<grid, 256, 0, st>>>(w, N, K, a, lda, T, nullptr, y, N, ggb_moe_groups{});
     }
     GGB_LAUNCH_CHECK();
     return GGB_OK;
@@ -982,6 +1005,19 @@ int ggb_op_hyper_mix_moe(int dt, float *xs, const float *y2, const int32_t *ws, 
     GGB_CHECK_ARG(ws && top > 0 && n_exp > 0 && n_identity >= 0 && n_identity <= n_exp && T_slots >= T, "hyper_mix_moe: bad arguments");
     return hyper_mix_launch(dt, xs, nullptr, nullptr, y2, ws + n_exp + 1 + T_slots * top, wt, idx, top, n_exp - n_identity, h_in, mix, coef, S, in_w, nw, eps, W, T,
                             rows, u_out, h);
+}
+
+int ggb_op_linear_relu2(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int64_t T, float *scratch, void *y) {
+    GGB_REQUIRE_INIT();
+    GGB_CHECK_DT(dt);
+    GGB_CHECK_ARG(w && a && y && N > 0 && K > 0 && T > 0 && lda >= K, "linear_relu2: bad shape N=%lld K=%lld T=%lld", (long long)N, (long long)K, (long long)T);
+    // shapes the tensor cores take: the product into scratch, then the activation; every other shape in one launch
+    if (dt == GGB_TYPE_BF16 && scratch && lda == K && ggb_gemm_dense_bf16_fits(N, K, T, N)) {
+        const int rc = ggb_gemm_dense_bf16(w, N, K, a, T, scratch, N);
+        return rc ? rc : ggb_op_act_rows(dt, scratch, N, T, N, 1, y);
+    }
+    if (dt == GGB_TYPE_BF16) return linear_relu2_launch((const __nv_bfloat16 *)w, N, K, (const __nv_bfloat16 *)a, lda, T, (__nv_bfloat16 *)y);
+    return linear_relu2_launch((const float *)w, N, K, (const float *)a, lda, T, (float *)y);
 }
 
 int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y) {

@@ -549,8 +549,7 @@ int kibilix_model::emit(int T, const int32_t *table, float *state, int n_want) {
         if (l.ff_kind) {
             KB_TRY(streams(w.hc2.in, w.norm2, nullptr, t, nullptr, h_));
             if (l.ff_kind == 1) {
-                KB_OP("op_linear", ggb_op_linear(dt_, w.up, l.ff, W, h_, W, t, gu_, l.ff));
-                KB_OP("op_act", ggb_op_act_rows(dt_, gu_, l.ff, t, l.ff, 1, act_));
+                KB_OP("op_linear", ggb_op_linear_relu2(dt_, w.up, l.ff, W, h_, W, t, gu_, act_));
                 KB_OP("op_linear", ggb_op_linear(dt_, w.down, W, l.ff, act_, l.ff, t, yb_, W));
             } else {
                 const kb_moe_cfg &E = l.moe;

@@ -314,6 +314,10 @@ int ggb_op_hyper_mix(int dt, float *xs, const float *x0, const float *y, const f
 int ggb_op_hyper_mix_moe(int dt, float *xs, const float *y2, const int32_t *ws, const float *wt, const int32_t *idx, int64_t T_slots, int top, int n_exp,
                          int n_identity, const void *h_in, const float *mix, const float *coef, int S, const float *in_w, const float *nw, float eps,
                          int64_t W, int64_t T, const int32_t *rows, float *u_out, void *h);
+/* y (dt, dense [T][N]) = relu(a w^T)^2: a feed-forward's first product with its activation.  One launch (the mat-vec or the
+ * tile kernel with the activation as its epilogue) except for the shapes the tensor cores take, which go through scratch
+ * (fp32 [T][N]; NULL: never) and ggb_op_act_rows */
+int ggb_op_linear_relu2(int dt, const void *w, int64_t N, int64_t K, const void *a, int64_t lda, int64_t T, float *scratch, void *y);
 /* y (dt, dense [T][F]) = act(x), x fp32 rows of stride ldx; act 0: as it is, 1: relu(x)^2 */
 int ggb_op_act_rows(int dt, const float *x, int64_t ldx, int64_t T, int64_t F, int act, void *y);
 

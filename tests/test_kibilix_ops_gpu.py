@@ -120,6 +120,16 @@ def test_act_rows_square_of_relu_and_strided_copy(gpu, dt):
         assert F.rel_err(from_dt(dt, y, (7, 37)), want) < (5e-3 if dt == BF16 else 1e-7)
 
 
+@pytest.mark.parametrize("dt", [F32, BF16])
+@pytest.mark.parametrize("T,N,K", [(1, 24, 40), (3, 17, 33), (8, 64, 128), (9, 24, 40), (70, 50, 22), (128, 256, 128)])
+def test_first_product_of_the_dense_feed_forward_with_its_activation(gpu, dt, T, N, K):
+    r = np.random.default_rng(T + N)
+    (wv, wu), (av, au) = as_dt(dt, r.standard_normal((N, K)) / np.sqrt(K)), as_dt(dt, r.standard_normal((T, K)))
+    y, scratch = zeros(gpu, T * N * 4), zeros(gpu, T * N * 4)
+    gpu.check(gpu.cuda_lib().ggb_op_linear_relu2(dt, dev(gpu, wu).ptr, N, K, dev(gpu, au).ptr, K, T, scratch.ptr, y.ptr), "linear_relu2")
+    assert F.rel_err(from_dt(dt, y, (T, N)), np.maximum(av @ wv.T, 0) ** 2) < (6e-3 if dt == BF16 else 3e-6)
+
+
 # ------------------------------------------------------------------------------------------------ chunked attention
 def cos_sin(freqs, n):
     a = np.arange(n)[:, None] * np.asarray(freqs)[None, :]
