@@ -204,26 +204,39 @@ __global__ void __launch_bounds__(32) moe_select_sigmoid_kernel(const float *__r
     select_sigmoid_warp(sm, sm + n_exp, sm + 2 * n_exp, corr, n_exp, top, n_groups, keep, blockIdx.x, threadIdx.x, idx, wt);
 }
 
-// few tokens (a step): logits and choice in ONE launch, a CTA per token, its warps an expert's logit each in turn.  With
-// row_src the slots are also listed as the mat-vec form of the grouped products reads them (slot s = row s: no order is
-// needed there), which stands in for moe_group_kernel.
+// few tokens (a step): logits and choice in ONE launch.  CTA (token, y) computes the logits of experts 8 y .. 8 y + 7, a warp
+// each, so that the router's rows are read by many SMs; the CTA that finishes last for its token (a counter per token, put
+// back to zero by that CTA) reads all logits back and chooses.  With row_src the slots are also listed as the mat-vec form
+// of the grouped products reads them (slot s = row s: no order is needed there), which stands in for moe_group_kernel.
 // SOFTMAX: the rule of select_softmax_warp instead (n_groups and keep unused)
+constexpr int kRouteStepTokens = 32, kRouteStepWarps = 8;
+__device__ unsigned int g_route_done[kRouteStepTokens];
+
 template <typename E, bool SOFTMAX>
-__global__ void __launch_bounds__(1024) moe_route_sigmoid_step_kernel(const E *__restrict__ h, int64_t W, const float *__restrict__ w,
+__global__ void __launch_bounds__(32 * kRouteStepWarps) moe_route_sigmoid_step_kernel(const E *__restrict__ h, int64_t W, const float *__restrict__ w,
                                                                      const float *__restrict__ corr, int n_exp, int top, int n_groups, int keep,
-                                                                     float *__restrict__ zg, int32_t *__restrict__ idx, float *__restrict__ wt,
+                                                                     float *zg, int32_t *__restrict__ idx, float *__restrict__ wt,
                                                                      int32_t *__restrict__ row_src, int32_t *__restrict__ inv,
                                                                      int32_t *__restrict__ row_expert) {
     extern __shared__ float sm[];
+    __shared__ bool last;
     const int64_t t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int e = warp; e < n_exp; e += (int)(blockDim.x >> 5)) {
+    const int e = (int)blockIdx.y * kRouteStepWarps + warp;
+    if (e < n_exp) {
         const float s = router_dot(h + t * W, w + (int64_t)e * W, W, lane);
         if (lane == 0) {
-            sm[e] = s;
             zg[t * n_exp + e] = s;
+            __threadfence(); // the logit is visible before this CTA is counted
         }
     }
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&g_route_done[t], 1u) == gridDim.y - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int i = threadIdx.x; i < n_exp; i += blockDim.x) sm[i] = __ldcg(zg + t * n_exp + i); // other CTAs wrote them: not through L1
+    if (threadIdx.x == 0) g_route_done[t] = 0; // the next launch starts from zero
     __syncthreads();
     if (warp != 0) return;
     if (SOFTMAX) select_softmax_warp(sm, sm + n_exp, corr, n_exp, top, t, lane, idx, wt);
@@ -395,13 +408,12 @@ int ggb_op_moe_route_sigmoid(int dt, const void *h, int64_t W, int64_t T, const 
         const int64_t n = T * top;
         const int mt = ggb_moe_max_tiles(n, n_exp);
         const bool lists = ws && ggb_moe_step_form(n);
-        const unsigned step_threads = 32u * (unsigned)std::min(32, std::max(n_exp, 1)); // a warp per expert, up to 32 at a time
         int32_t *row_src = lists ? ws + n_exp + 1 : nullptr, *inv = lists ? row_src + n : nullptr, *row_expert = lists ? inv + n + 2 * mt + 1 : nullptr;
         if (dt == GGB_TYPE_BF16)
-            moe_route_sigmoid_step_kernel<__nv_bfloat16, false><<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, w_router, correction, n_exp, top, n_groups,
+            moe_route_sigmoid_step_kernel<__nv_bfloat16, false><<<dim3((unsigned)T, (unsigned)((n_exp + kRouteStepWarps - 1) / kRouteStepWarps)), 32 * kRouteStepWarps, smem, ggb_cuda_stream()>>>((const __nv_bfloat16 *)h, W, w_router, correction, n_exp, top, n_groups,
                                                                                          keep, logits, idx, wt, row_src, inv, row_expert);
         else
-            moe_route_sigmoid_step_kernel<float, false><<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>((const float *)h, W, w_router, correction, n_exp, top, n_groups, keep,
+            moe_route_sigmoid_step_kernel<float, false><<<dim3((unsigned)T, (unsigned)((n_exp + kRouteStepWarps - 1) / kRouteStepWarps)), 32 * kRouteStepWarps, smem, ggb_cuda_stream()>>>((const float *)h, W, w_router, correction, n_exp, top, n_groups, keep,
                                                                                          logits, idx, wt, row_src, inv, row_expert);
         GGB_LAUNCH_CHECK();
         return GGB_OK;
@@ -429,13 +441,12 @@ int ggb_op_moe_route_softmax(int dt, const void *h, int64_t W, int64_t T, const 
         const int64_t n = T * top;
         const int mt = ggb_moe_max_tiles(n, n_exp);
         const bool lists = ws && ggb_moe_step_form(n);
-        const unsigned step_threads = 32u * (unsigned)std::min(32, std::max(n_exp, 1));
         int32_t *row_src = lists ? ws + n_exp + 1 : nullptr, *inv = lists ? row_src + n : nullptr, *row_expert = lists ? inv + n + 2 * mt + 1 : nullptr;
         if (dt == GGB_TYPE_BF16)
-            moe_route_sigmoid_step_kernel<__nv_bfloat16, true><<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>(
+            moe_route_sigmoid_step_kernel<__nv_bfloat16, true><<<dim3((unsigned)T, (unsigned)((n_exp + kRouteStepWarps - 1) / kRouteStepWarps)), 32 * kRouteStepWarps, smem, ggb_cuda_stream()>>>(
                 (const __nv_bfloat16 *)h, W, w_router, correction, n_exp, top, 1, 1, logits, idx, wt, row_src, inv, row_expert);
         else
-            moe_route_sigmoid_step_kernel<float, true><<<(unsigned)T, step_threads, smem, ggb_cuda_stream()>>>(
+            moe_route_sigmoid_step_kernel<float, true><<<dim3((unsigned)T, (unsigned)((n_exp + kRouteStepWarps - 1) / kRouteStepWarps)), 32 * kRouteStepWarps, smem, ggb_cuda_stream()>>>(
                 (const float *)h, W, w_router, correction, n_exp, top, 1, 1, logits, idx, wt, row_src, inv, row_expert);
         GGB_LAUNCH_CHECK();
         return GGB_OK;
