@@ -145,6 +145,12 @@ OTHER = {
                                        vocab=64, width=12, streams=5, loop=(1, 2, 2)),
     "only_delta": lambda: F.config([F.layer("channel_delta", F.delta(), F.moe(experts=3, identity=1, top=2)), F.layer("channel_delta", F.delta(heads=3, kv_heads=3, dim=5, vdim=3, conv=4))],
                                    vocab=19, width=20, streams=2, buckets=3, loop=(0, 1, 1)),
+    # seven streams (the scalar form of the stream kernel), low-rank projections too wide for the fused pair (rank 800, 801)
+    "seven_streams_wide_rank": lambda: F.config([F.layer("channel_delta", F.delta(heads=2, kv_heads=1, dim=8, vdim=6, conv=2), F.moe(experts=3, identity=2, top=2, ff=6)),
+                                                 F.layer("attention", F.attention(heads=2, kv_heads=1, dim=8, vdim=4, chunk=7), F.dense(12))],
+                                                vocab=23, width=24, streams=7, buckets=5),
+    "sixteen_streams": lambda: F.config([F.layer("attention", F.attention(heads=2, kv_heads=2, dim=6, vdim=6, chunk=0, dims=None), F.dense(10)),
+                                         F.layer("channel_delta", F.delta(heads=2, kv_heads=2, dim=6, vdim=4, conv=3))], vocab=29, width=18, streams=16, loop=(0, 2, 2)),
     "wide": lambda: F.config([F.layer("channel_delta", F.delta(heads=4, kv_heads=2, dim=128, vdim=48, conv=4), F.moe(experts=6, identity=1, top=2, ff=40, limit=1.1)),
                               F.layer("attention", F.attention(heads=4, kv_heads=2, dim=32, vdim=64, chunk=70, dims=16), F.dense(160)),
                               F.layer("attention", F.attention(heads=2, kv_heads=1, dim=64, vdim=34, chunk=9, dims=None, scaling=False)),
@@ -157,7 +163,7 @@ OTHER = {
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes_and_optional_parts(gpu, tmp_path, name, dtype):
     cfg = OTHER[name]()
-    d, W = F.make_model(str(tmp_path / name), cfg, seed=3, rank=4 if name != "wide" else 24)
+    d, W = F.make_model(str(tmp_path / name), cfg, seed=3, rank={"wide": 24, "seven_streams_wide_rank": 800}.get(name, 4))
     toks = np.random.default_rng(4).integers(0, cfg["vocab"], 140)
     want = KP.forward(toks, W, cfg)
     eng = gpu.Engine(d, dtype=dtype, max_tokens=300, page_size=16)
