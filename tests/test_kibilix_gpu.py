@@ -228,3 +228,32 @@ def test_greedy_generation_through_the_engine(gpu, small):
     eng.end("g")
     assert eng.stats()["live_seqs"] == 0
     eng.close()
+
+
+def test_the_command_line_programs_replay_a_trace_and_generate(gpu, small, tmp_path):
+    """bin/trace_run as its user starts it: steps on standard input, logits in files, a line per step; two requests one after the
+    other with the second one's id used again; bin/lm_generate gives the ids Engine.generate gives."""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg, d, W, toks, want = small
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "out")
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:40].tolist(), "want": [0, 39]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[40:42].tolist(), "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[42:43].tolist(), "want": [0]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": toks[:5].tolist(), "want": [4]}], "end": ["a"]}]
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out", out, "--max-tokens", "64"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [line for line in p.stdout.split("\n") if line.startswith("done")] == ["done %d" % i for i in range(4)]
+    assert not os.path.exists(os.path.join(out, "1.f32"))
+    got = {i: np.fromfile(os.path.join(out, "%d.f32" % i), dtype="<f4").reshape(-1, cfg["vocab"]) for i in (0, 2, 3)}
+    assert F.close_enough(got[0], want[[0, 39]], "float32") and F.close_enough(got[2], want[[42]], "float32") and F.close_enough(got[3], want[[4]], "float32")
+    g = subprocess.run([sys.executable, os.path.join(root, "bin", "lm_generate"), "--model", d, "--dtype", "float32", "--prompt", ",".join(map(str, toks[:12])), "--new", "9"],
+                       capture_output=True, text=True, timeout=600)
+    assert g.returncode == 0, g.stderr[-2000:]
+    eng = gpu.Engine(d, dtype="float32", max_tokens=128)
+    assert [int(t) for t in g.stdout.strip().split("\n")[-1].split(",")] == eng.generate("g", toks[:12], 9).tolist()
+    eng.close()
